@@ -2,9 +2,10 @@ from .model_config import ConfigError, ModelConfig, read_config_json, write_conf
 from .qwen3_config import Qwen3Config
 from .ganidra_config import GanidraConfig
 from .besavik_config import BesavikConfig
+from .merudra_config import MerudraConfig
 from .engine_config import EngineConfig, parse_dtype
 from .presets import PRESETS, preset_config_dict, preset_init
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "GanidraConfig", "BesavikConfig", "read_config_json",
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "GanidraConfig", "BesavikConfig", "MerudraConfig", "read_config_json",
            "write_config_json", "EngineConfig", "parse_dtype", "PRESETS",
            "preset_config_dict", "preset_init"]

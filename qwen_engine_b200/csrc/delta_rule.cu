@@ -8,6 +8,8 @@
 // attention).  Per token a column needs k.s and q.s of the decayed column; q.k is the same for all columns, and
 // o = q.s + (q.k) u, so the three sums are formed in one pass and reduced together.  The order of every sum depends on
 // the sizes alone: a prompt cut anywhere gives the same bits.  g null: one constant decay per head (head_decay) or none.
+// hd_in [T, H] (compute type): on top of either, one decay per token and head that the CTA forms itself while it stages
+// the token, exp(-exp(hd_rate[h]) softplus(hd_in[t, h] + hd_bias[h])) in float32.
 // q, k [T, G dk] (head h reads group h / (H / G)), v [T, H dv], g [T, H dk], beta [T, H]: float32; state float32
 // [slot][head][value channel][key channel]; a request without context starts from zero whatever its slot holds.
 #include "common.cuh"
@@ -142,6 +144,7 @@ struct DeltaArgs {
   long ldq, ldk, ldv, ldg;                                          // row strides in floats
   const void* beta; long ld_beta; int beta_dtype;                   // [T, H] before the sigmoid, compute type; null: beta = 1
   const float* head_decay;                                          // with g null: one decay per head, or null for none
+  const void* hd_in; long ld_hd; const float* hd_rate; const float* hd_bias;   // a decay per token and head, formed here; null: none
   float* state; const int* cu_q; const int* ctx_lens; const int* slot_ids; float* out;
   int H, G, dk, dv, L, VT, write_state, delta, chunk;
 };
@@ -278,6 +281,15 @@ delta_rule_scan_kernel(DeltaArgs A) {
         bt = 1.f / (1.f + expf(-z));
       }
       b[(size_t)t * tok_w + 3 * row_w + ((VT + 3) & ~3)] = bt;
+      // the token's decay of the whole head (one where the head has none)
+      float gd = 1.f;
+      if (A.hd_in) {
+        const size_t at = (size_t)(row0 + t_first + t) * A.ld_hd + head;
+        const float z = (A.beta_dtype == QE_DTYPE_F32 ? ((const float*)A.hd_in)[at] : __bfloat162float(((const __nv_bfloat16*)A.hd_in)[at]))
+                        + A.hd_bias[head];
+        gd = expf(-expf(A.hd_rate[head]) * (fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)))));
+      }
+      b[(size_t)t * tok_w + 3 * row_w + ((VT + 3) & ~3) + 1] = gd;
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -299,12 +311,13 @@ delta_rule_scan_kernel(DeltaArgs A) {
       float* o = A.out + (size_t)(row0 + ch * A.chunk) * o_ld + (size_t)head * dv + j;
       for (int t = 0; t < rows; ++t) {
         float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f, qk0 = 0.f, qk1 = 0.f;
+        const float gd = rv[((VT + 3) & ~3) + 1];          // (times one changes no bit)
 #pragma unroll
         for (int i = 0; i < DC; i += 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(r + i);
           const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
           const float4 g4 = *reinterpret_cast<const float4*>(r + 2 * row_w + i);
-          s[i] *= g4.x; s[i + 1] *= g4.y; s[i + 2] *= g4.z; s[i + 3] *= g4.w;
+          s[i] *= g4.x * gd; s[i + 1] *= g4.y * gd; s[i + 2] *= g4.z * gd; s[i + 3] *= g4.w * gd;
           ks0 = fmaf(k4.x, s[i], ks0);     qs0 = fmaf(q4.x, s[i], qs0);     qk0 = fmaf(q4.x, k4.x, qk0);
           ks1 = fmaf(k4.y, s[i + 1], ks1); qs1 = fmaf(q4.y, s[i + 1], qs1); qk1 = fmaf(q4.y, k4.y, qk1);
           ks0 = fmaf(k4.z, s[i + 2], ks0); qs0 = fmaf(q4.z, s[i + 2], qs0); qk0 = fmaf(q4.z, k4.z, qk0);
@@ -346,8 +359,10 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
                                   const float* g, long ldg, const void* beta,
                                   long ld_beta, int beta_dtype, const float* head_decay, float* state, const int* cu_q,
                                   const int* ctx_lens, const int* slot_ids, float* out, int R, int H, int G, int dk, int dv,
-                                  int write_state, int delta, cudaStream_t stream) {
+                                  int write_state, int delta, const void* hd_in, long ld_hd, const float* hd_rate,
+                                  const float* hd_bias, cudaStream_t stream) {
   if (R <= 0) return 0;
+  if (hd_in && (!hd_rate || !hd_bias)) QE_REFUSE("delta_rule_scan: a decay per token and head needs its rate and bias");
   if (dk < 1 || dk > 1024 || dv < 1) QE_REFUSE("delta_rule_scan: key size %d must be 1..1024, value size %d positive", dk, dv);
   if (H < 1 || H > 65535 || G < 1 || H % G) QE_REFUSE("delta_rule_scan: %d heads over %d key heads", H, G);
   int DC = dk <= 16 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
@@ -360,6 +375,7 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
   if (L > 32) QE_REFUSE("delta_rule_scan: key size %d is too large", dk);
   DeltaArgs A;
   A.q = q; A.k = k; A.v = v; A.g = g; A.ldq = ldq; A.ldk = ldk; A.ldv = ldv; A.ldg = g ? ldg : 0; A.beta = beta; A.ld_beta = ld_beta; A.beta_dtype = beta_dtype; A.head_decay = head_decay;
+  A.hd_in = hd_in; A.ld_hd = ld_hd; A.hd_rate = hd_rate; A.hd_bias = hd_bias;
   A.state = state; A.cu_q = cu_q; A.ctx_lens = ctx_lens; A.slot_ids = slot_ids; A.out = out;
   A.H = H; A.G = G; A.dk = dk; A.dv = dv; A.L = L; A.write_state = write_state; A.delta = delta;
   int VT = DR_MAX_THREADS / L;

@@ -530,6 +530,82 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
 }
 
 // ---------------------------------------------------------------------------------------
+// Attention whose values are its keys as projected.  One warp per (token, head) of the q and k heads that lead the
+// rows of a stacked projection output: the bias is added; a key head as it then is goes to the token's slot of the
+// value plane; the head is divided by its root mean square (no weight); a query head is multiplied by the temperature
+// of its position p, 1 + coef ln(floor((p + 1) / every) + 1) (every = 0: none); written back in place, a key head
+// also to the key plane.  Float32 arithmetic, each output rounded once.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_bias_norm_kv_write_kernel(T* __restrict__ proj, long stride, const int* __restrict__ positions,
+                                             const float* __restrict__ q_bias, const float* __restrict__ k_bias, float eps,
+                                             float temp_coef, int temp_every, T* __restrict__ pages,
+                                             const int* __restrict__ slot_mapping, int T_tokens, int Hq, int Hkv, int D,
+                                             int page_size, int write_kv) {
+  extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_total = Hq + Hkv;
+  const long item = (long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long)T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int head = (int)(item % heads_total);
+  float* buf = smem + (size_t)warp * D;
+  const bool is_q = head < Hq;
+  const int h = is_q ? head : head - Hq;
+  T* x = proj + (size_t)t * stride + (size_t)head * D;
+  const float* bias = is_q ? (q_bias ? q_bias + (size_t)h * D : nullptr) : (k_bias ? k_bias + (size_t)h * D : nullptr);
+  T* key_dst = nullptr;
+  T* value_dst = nullptr;
+  if (!is_q && write_kv) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    key_dst = pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D;
+    value_dst = pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D;
+  }
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    float val = to_f32(x[d]);
+    if (bias) val = to_f32(from_f32<T>(val + bias[d]));        // the projection's output with its bias, as stored
+    if (value_dst) value_dst[d] = from_f32<T>(val);
+    buf[d] = val;
+    ss += val * val;
+  }
+  ss = warp_sum(ss);
+  float f = rsqrtf(ss / (float)D + eps);
+  if (is_q && temp_every > 0) f *= 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.f);
+  for (int d = lane; d < D; d += 32) {
+    const T r = from_f32<T>(buf[d] * f);
+    x[d] = r;
+    if (key_dst) key_dst[d] = r;
+  }
+}
+
+extern "C" int qe_qk_bias_norm_kv_write(void* proj, long stride, const int* positions, const float* q_bias, const float* k_bias,
+                                        float eps, float temp_coef, int temp_every, void* pages, const int* slot_mapping, int T,
+                                        int Hq, int Hkv, int D, int page_size, int write_kv, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D > QKR_MAX_D) QE_REFUSE("qk_bias_norm_kv_write: head_dim %d is above %d", D, QKR_MAX_D);
+  if (write_kv && (!pages || !slot_mapping)) QE_REFUSE("qk_bias_norm_kv_write: cache write without cache");
+  if (temp_every < 0) QE_REFUSE("qk_bias_norm_kv_write: the temperature's step %d is negative", temp_every);
+  const int warps = 4;
+  const long items = (long)T * (Hq + Hkv);
+  if (items > 0x7fffff00L) QE_REFUSE("qk_bias_norm_kv_write: %d tokens x %d heads are too many for one launch", T, Hq + Hkv);
+  const int blocks = (int)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * D * sizeof(float);
+#define QKB(TT) qe_launch(qk_bias_norm_kv_write_kernel<TT>, dim3(blocks), dim3(warps * 32), smem, stream, (TT*)proj, stride, \
+                          positions, q_bias, k_bias, eps, temp_coef, temp_every, (TT*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv)
+  if (dtype == QE_DTYPE_F32) QKB(float);
+  else if (dtype == QE_DTYPE_BF16) QKB(__nv_bfloat16);
+  else QE_REFUSE("qk_bias_norm_kv_write: unknown dtype %d", dtype);
+#undef QKB
+  QE_CHECK_LAUNCH("qk_bias_norm_kv_write");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // dst[rows[i]] = src[src_index[i]]: token ids that the step before this one sampled and that the host
 // has not read yet are put into this step's token list on the device (a step launched ahead).
 // ---------------------------------------------------------------------------------------

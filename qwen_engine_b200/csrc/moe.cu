@@ -2,13 +2,15 @@
 // of each expert.
 //
 //   qe_moe_route       z = W_r h + b in float32 per token; the `top` largest (the lower index wins a tie); weights =
-//                      softmax over the chosen logits alone
+//                      softmax over the chosen logits alone.  Second scoring: s = softmax(z) over all outputs, the `top`
+//                      largest of s + correction are chosen, the weights are their s as it is
 //   qe_moe_sort        the (token, choice) pairs ordered by expert: offsets[E + 1], the pairs of every expert side by
 //                      side, and where each pair went.  One CTA.  Which pair of an expert comes first is not fixed
 //                      (atomics); nothing depends on it, since every pair's row is computed alone
 //   qe_moe_gate_up     act[p, :] = glu(W_gate_e x_t, W_up_e x_t) for the pair p = (t, e) in sorted order
 //   qe_moe_down        y[p, :] = W_down_e act[p, :], float32
-//   qe_moe_combine     out[t, :] = sum over the token's choices, in their order, of weight x y[place of the pair]
+//   qe_moe_combine     out[t, :] = sum over the token's choices, in their order, of weight x y[place of the pair]; a choice
+//                      at or beyond the experts that have weights stands for an expert that hands its input on: x[t, :]
 //
 // The grids of the two products are sized for the worst case (every expert's rows end in a tile of their own):
 // nothing of a step's shape depends on the routing, so a step can be replayed from a CUDA graph.
@@ -21,7 +23,8 @@
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                 int* __restrict__ top_idx, float* __restrict__ top_w, int T_tokens, int W, int E, int top) {
+                 int* __restrict__ top_idx, float* __restrict__ top_w, int T_tokens, int W, int E, int top, int scoring,
+                 const float* __restrict__ correction) {
   extern __shared__ float route_smem[];             // the token's row [W], then its logits [E]
   float* xs = route_smem;
   float* z = route_smem + ((W + 3) & ~3);
@@ -62,6 +65,36 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
   }
   __syncthreads();
   if (warp != 0) return;
+  if (scoring == 1) {
+    // scores over all outputs: the largest logit and the sum of the exponentials lane by lane, then over the lanes in a
+    // fixed order; the choice looks at score + correction, the weight is the score
+    float* sc = z + E;                               // the scores, behind the logits (which become the choice values)
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) { const float p = sc[e] * inv; sc[e] = p; z[e] = p + (correction ? correction[e] : 0.f); }
+    __syncwarp();
+    for (int j = 0; j < top; ++j) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) { const float v = z[e]; if (v > best) { best = v; at = e; } }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at == 0x7fffffff) at = 0;
+      if (lane == 0) { top_idx[(size_t)t * top + j] = at; top_w[(size_t)t * top + j] = sc[at]; z[at] = -INFINITY; }
+      __syncwarp();
+    }
+    return;
+  }
   float chosen[MOE_MAX_TOP];
   float zmax = 0.f;
   for (int j = 0; j < top; ++j) {
@@ -86,10 +119,11 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
 }
 
 extern "C" int qe_moe_route(const void* x, const float* w, const float* bias, int* top_idx, float* top_w, int T, int W,
-                            int E, int top, int dtype, cudaStream_t stream) {
+                            int E, int top, int dtype, int scoring, const float* correction, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 1 || E > MOE_MAX_E || top < 1 || top > MOE_MAX_TOP || top > E) QE_REFUSE("moe_route: %d of %d experts", top, E);
-  const size_t smem = ((size_t)((W + 3) & ~3) + E) * sizeof(float);
+  if (scoring != 0 && scoring != 1) QE_REFUSE("moe_route: unknown scoring %d", scoring);
+  const size_t smem = ((size_t)((W + 3) & ~3) + 2 * (size_t)E) * sizeof(float);
   if (smem > 160 * 1024) QE_REFUSE("moe_route: a row of %d channels does not fit shared memory", W);
   static bool configured = false;
   if (!configured) {
@@ -98,7 +132,7 @@ extern "C" int qe_moe_route(const void* x, const float* w, const float* bias, in
     if (e != cudaSuccess) QE_REFUSE("moe_route: shared memory: %s", cudaGetErrorString(e));
     configured = true;
   }
-#define MR(TT) qe_launch(moe_route_kernel<TT>, dim3(T), dim3(128), smem, stream, (const TT*)x, w, bias, top_idx, top_w, T, W, E, top)
+#define MR(TT) qe_launch(moe_route_kernel<TT>, dim3(T), dim3(128), smem, stream, (const TT*)x, w, bias, top_idx, top_w, T, W, E, top, scoring, correction)
   if (dtype == QE_DTYPE_F32) MR(float);
   else if (dtype == QE_DTYPE_BF16) MR(__nv_bfloat16);
   else QE_REFUSE("moe_route: unknown dtype %d", dtype);
@@ -320,10 +354,11 @@ extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets
   return 0;
 }
 
-template <typename T>
+template <typename T, typename TX>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of_pair,
                                    const float* __restrict__ top_w, T* __restrict__ out, long total, int N, int top,
-                                   int shares, long share_stride) {
+                                   int shares, long share_stride, const int* __restrict__ top_idx, int E,
+                                   const TX* __restrict__ x) {
   pdl_launch_dependents();
   pdl_wait();
   for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
@@ -331,24 +366,32 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     const int n = (int)(e - t * N);
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
-      const float* src = y + (size_t)place_of_pair[t * top + j] * N + n;
-      float v = src[0];
-      for (int z = 1; z < shares; ++z) v += src[(size_t)z * share_stride];
+      float v;
+      if (top_idx && top_idx[t * top + j] >= E) {
+        v = to_f32(x[e]);                            // an expert that hands its input on
+      } else {
+        const float* src = y + (size_t)place_of_pair[t * top + j] * N + n;
+        v = src[0];
+        for (int z = 1; z < shares; ++z) v += src[(size_t)z * share_stride];
+      }
       acc = fmaf(top_w[t * top + j], v, acc);
     }
     out[e] = from_f32<T>(acc);
   }
 }
 
+// top_idx, E, x (null: every choice has weights): choices at or beyond E hand x[t] on (x [T, N] in x_dtype)
 extern "C" int qe_moe_combine(const float* y, const int* place_of_pair, const float* top_w, void* out, int T, int N, int top,
-                              int shares, int dtype, cudaStream_t stream) {
+                              int shares, int dtype, const int* top_idx, int E, const void* x, int x_dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if ((top_idx != nullptr) != (x != nullptr)) QE_REFUSE("moe_combine: identity experts need the choices and the input");
   const long total = (long)T * N;
   const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-#define MC(TT) qe_launch(moe_combine_kernel<TT>, dim3(blocks), dim3(256), 0, stream, y, place_of_pair, top_w, (TT*)out, total, N, top, shares, (long)T * top * N)
-  if (dtype == QE_DTYPE_F32) MC(float);
-  else if (dtype == QE_DTYPE_BF16) MC(__nv_bfloat16);
-  else QE_REFUSE("moe_combine: unknown dtype %d", dtype);
+#define MC(TT, TX) qe_launch(moe_combine_kernel<TT, TX>, dim3(blocks), dim3(256), 0, stream, y, place_of_pair, top_w, (TT*)out, total, N, top, shares, (long)T * top * N, top_idx, E, (const TX*)x)
+  if (dtype == QE_DTYPE_F32 && (!x || x_dtype == QE_DTYPE_F32)) MC(float, float);
+  else if (dtype == QE_DTYPE_BF16 && (!x || x_dtype == QE_DTYPE_BF16)) MC(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == QE_DTYPE_F32 && x_dtype == QE_DTYPE_BF16) MC(float, __nv_bfloat16);
+  else QE_REFUSE("moe_combine: unknown dtypes %d, %d", dtype, x_dtype);
 #undef MC
   QE_CHECK_LAUNCH("moe_combine");
   return 0;

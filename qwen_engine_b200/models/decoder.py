@@ -67,6 +67,19 @@ class ModelLayout:
     embed_scale: float = 1.0    # the embedding output is the table's row times this (the head uses the table as it is)
     embed_norm: Optional[PartSpec] = None         # a norm that the embedding output passes before the first layer ...
     embed_norm_prefix: str = "embed.norm"         # ... and the prefix of its tensors
+    layer_history: bool = False                   # a step keeps the embedding output and every layer run's result (blocks
+                                                  # that read earlier layers' results find them in ctx.extras)
+
+
+@dataclass
+class LayerHistory:
+    """The results of a step's layer runs so far, for arrangements that read them again: ``results`` float32
+    [runs + 1, T, H] (entry 0 is the embedding output, entry i + 1 the result of run i, written by its block),
+    ``run`` the index of the run in progress, ``mixed`` a float32 [T, H] buffer for what goes on to the next run."""
+
+    results: torch.Tensor
+    mixed: torch.Tensor
+    run: int = 0
 
 
 class DecoderModel:
@@ -87,9 +100,9 @@ class DecoderModel:
                 raise ValueError(f"plan names layer {e.layer}, the model has {len(self.blocks)}")
             if not e.slots:
                 continue
-            needs = self.blocks[e.layer].mixer.cache_specs()
+            needs = self.blocks[e.layer].cache_specs()
             if len(needs) != len(e.slots):
-                raise ValueError(f"plan gives layer {e.layer} {len(e.slots)} cache slot(s) but its mixer keeps {len(needs)} cache(s)")
+                raise ValueError(f"plan gives layer {e.layer} {len(e.slots)} cache slot(s) but it keeps {len(needs)} cache(s)")
             for slot, spec in zip(e.slots, needs):
                 if specs[slot] is not None and specs[slot] != spec:
                     raise ValueError(f"cache slot {slot} is used by layers with different needs")
@@ -179,6 +192,13 @@ class DecoderModel:
         lo = self.layout
         T, H = ctx.num_tokens, lo.hidden_size
         stream = ops.ResidualStream.for_step(ctx.arena.alloc, T, H, ctx.dtype)
+        history = None
+        if lo.layer_history:
+            # the stream starts as entry 0 of the runs' results; a block that mixes them hands on ``mixed``
+            history = LayerHistory(ctx.arena.alloc_step((len(lo.plan) + 1, T, H), torch.float32),
+                                   ctx.arena.alloc_step((T, H), torch.float32))
+            stream.resid, stream.ssq = history.results[0], None
+            ctx.extras["layer_history"] = history
         if self.embed_norm is None:
             ops.embedding(ctx.token_ids, self.embed, stream, scale=lo.embed_scale)
         else:
@@ -207,6 +227,8 @@ class DecoderModel:
             # and the weights that the step reads first after this block
             nxt = lo.plan[i + 1].layer if i + 1 < len(lo.plan) else None
             ctx.extras["weights_after_ffn"] = self.blocks[nxt].first_weights() if nxt is not None else None
+            if history is not None:
+                history.run = i
             self.blocks[entry.layer].forward(ctx, stream, view, group, entry.write_cache)
         ctx.extras["next_cache"] = ctx.extras["weights_after_ffn"] = None
         if ctx.num_logit_rows == 0:

@@ -1367,12 +1367,15 @@ def unit_norm(x: torch.Tensor, num_heads: int, head_dim: int, eps: float, scale:
 
 def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                     state: torch.Tensor, ctx, out: torch.Tensor, num_heads: int, num_key_heads: int, key_dim: int,
-                    value_dim: int, write_state: bool = True) -> None:
+                    value_dim: int, write_state: bool = True, head_decay=None) -> None:
     """The gated delta rule per head over the step's tokens of every request, from the state its slot holds:
     S <- diag(g_t) S; u = sigmoid(beta_t) (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.
     q, k float32 [T, G dk] (head h reads group h // (H / G)), v float32 [T, H dv], g float32 [T, H dk] (None: no
-    decay), beta [T, H] before its sigmoid in the compute type (rows may be strided), state float32
-    [slots, H, dv, dk], out float32 [T, H dv].  Rows of q, k, v and g may be strided."""
+    decay per channel), beta [T, H] before its sigmoid in the compute type (rows may be strided), state float32
+    [slots, H, dv, dk], out float32 [T, H dv].  Rows of q, k, v and g may be strided.
+    ``head_decay`` = (a, log_rate, bias) in the place of ``g``: one decay per token and head that the scan forms
+    itself in float32, exp(-exp(log_rate[h]) softplus(a[t, h] + bias[h])), a [T, H] in the compute type (rows may
+    be strided), log_rate and bias float32 [H]."""
     H, G, dk, dv = num_heads, num_key_heads, key_dim, value_dim
     T = q.shape[0]
     for t, name, width in ((q, "q", G * dk), (k, "k", G * dk), (v, "v", H * dv)) + (((g, "g", H * dk),) if g is not None else ()):
@@ -1383,34 +1386,56 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: Option
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dv, dk),
           "delta_rule_scan: state must be float32 [slots, H, dv, dk]")
     _need(out.shape == (T, H * dv) and out.dtype == torch.float32 and out.is_contiguous(), "delta_rule_scan: out must be float32 [T, H dv]")
+    da = rate = dbias = None
+    if head_decay is not None:
+        da, rate, dbias = head_decay
+        _need(g is None, "delta_rule_scan: a decay per channel or one per head, not both")
+        _rows(da, "delta_rule_scan: the head decay's input")
+        _need(da.shape == (T, H) and da.dtype == beta.dtype, "delta_rule_scan: the head decay's input must be [T, H] in beta's type")
+        for t_, name in ((rate, "log_rate"), (dbias, "bias")):
+            _need(t_.dtype == torch.float32 and t_.shape == (H,) and t_.is_contiguous(), f"delta_rule_scan: the head decay's {name} must be float32 [H]")
     _check(lib().qe_delta_rule_scan(_ptr(q), ctypes.c_long(q.stride(0)), _ptr(k), ctypes.c_long(k.stride(0)), _ptr(v),
                                     ctypes.c_long(v.stride(0)), _ptr(g), ctypes.c_long(g.stride(0) if g is not None else 0),
                                     _ptr(beta), ctypes.c_long(beta.stride(0)), _dt(beta),
                                     ctypes.c_void_p(0), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(ctx.slot_ids),
-                                    _ptr(out), int(ctx.num_reqs), H, G, dk, dv, int(bool(write_state)), 1, _stream()),
+                                    _ptr(out), int(ctx.num_reqs), H, G, dk, dv, int(bool(write_state)), 1,
+                                    _ptr(da), ctypes.c_long(da.stride(0) if da is not None else 0), _ptr(rate), _ptr(dbias),
+                                    _stream()),
            "delta_rule_scan")
 
 
-def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], top_idx: torch.Tensor, top_w: torch.Tensor) -> None:
-    """Router of routed experts: z = w x[t] + bias in float32 (x in the compute type, w float32 [E, W]); the ``top``
-    largest logits' experts into top_idx int32 [T, top] (the lower index wins a tie) and the softmax over those
-    logits alone into top_w float32 [T, top]."""
+ROUTER_SCORINGS = {"softmax_chosen": 0, "softmax_all": 1}
+
+
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], top_idx: torch.Tensor, top_w: torch.Tensor,
+              scoring: str = "softmax_chosen", correction: Optional[torch.Tensor] = None) -> None:
+    """Router of routed experts: z = w x[t] + bias in float32 (x in the compute type, w float32 [E, W]).
+    ``softmax_chosen``: the ``top`` largest logits' experts into top_idx int32 [T, top] (the lower index wins a tie)
+    and the softmax over those logits alone into top_w float32 [T, top].
+    ``softmax_all``: s = softmax(z) over all E outputs; the ``top`` largest of s + correction (float32 [E], optional)
+    are chosen, and their weights are their s as it is (not made to sum to one)."""
     T, W = x.shape
     E = w.shape[0]
     top = top_idx.shape[1]
+    _need(scoring in ROUTER_SCORINGS, f"moe_route: unknown scoring {scoring!r}; known: {sorted(ROUTER_SCORINGS)}")
     _need(x.is_contiguous() and w.dtype == torch.float32 and w.shape == (E, W) and w.is_contiguous(), "moe_route: w must be float32 [E, W]")
     _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (E,)), "moe_route: bias must be float32 [E]")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.shape == (E,) and correction.is_contiguous()
+                                 and scoring == "softmax_all"), "moe_route: correction must be float32 [E], with softmax_all")
     _need(top_idx.shape == (T, top) and top_idx.dtype == torch.int32 and top_idx.is_contiguous()
           and top_w.shape == (T, top) and top_w.dtype == torch.float32 and top_w.is_contiguous(), "moe_route: outputs [T, top]")
-    _check(lib().qe_moe_route(_ptr(x), _ptr(w), _ptr(bias), _ptr(top_idx), _ptr(top_w), T, W, E, top, _dt(x), _stream()), "moe_route")
+    _check(lib().qe_moe_route(_ptr(x), _ptr(w), _ptr(bias), _ptr(top_idx), _ptr(top_w), T, W, E, top, _dt(x),
+                              ROUTER_SCORINGS[scoring], _ptr(correction), _stream()), "moe_route")
 
 
 def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                out: torch.Tensor, activation, alloc) -> None:
+                out: torch.Tensor, activation, alloc, num_identity: int = 0) -> None:
     """out[t] = sum_j top_w[t, j] * W_down[e] glu(W_gate[e] x[t], W_up[e] x[t]) with e = top_idx[t, j]: the pairs are
     ordered by expert on the device, each expert's rows run as tiles of two grouped products, and the token's choices
     are summed in their order.  w_gate_up [E, 2 I, K] (gate rows, then up rows), w_down [E, N, I]; ``alloc(shape,
-    dtype)`` gives scratch memory.  Nothing of the launches depends on the routing."""
+    dtype)`` gives scratch memory.  Nothing of the launches depends on the routing.
+    ``num_identity``: top_idx may also name E .. E + num_identity - 1, experts without weights whose output is
+    x[t] itself (N = K then); their pairs are ordered behind the others and only the weighted sum looks at them."""
     T, K = x.shape
     E, I2, _ = w_gate_up.shape
     I, N, top = I2 // 2, w_down.shape[1], top_idx.shape[1]
@@ -1418,10 +1443,11 @@ def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_g
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.shape == (E, 2 * I, K)
           and w_down.shape == (E, N, I) and x.dtype == w_gate_up.dtype == w_down.dtype, "moe_experts: w_gate_up [E, 2 I, K], w_down [E, N, I] in x's dtype")
     _need(out.shape == (T, N) and out.is_contiguous(), "moe_experts: out must be [T, N]")
-    offsets = alloc((E + 1,), torch.int32)
+    _need(num_identity >= 0 and (num_identity == 0 or N == K), "moe_experts: identity experts need outputs of the input's width")
+    offsets = alloc((E + num_identity + 1,), torch.int32)
     sorted_pair = alloc((P,), torch.int32)
     place = alloc((P,), torch.int32)
-    _check(lib().qe_moe_sort(_ptr(top_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(place), P, E, _stream()), "moe_sort")
+    _check(lib().qe_moe_sort(_ptr(top_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(place), P, E + num_identity, _stream()), "moe_sort")
     act = alloc((P, I), x.dtype)
     _check(lib().qe_moe_gate_up(_ptr(x), _ptr(w_gate_up), _ptr(offsets), _ptr(sorted_pair), _ptr(act), P, E, I, K, top,
                                 gate_code(activation), _dt(x), _stream()), "moe_gate_up")
@@ -1430,7 +1456,9 @@ def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_g
     shares = int(lib().qe_moe_down_shares(P, I, _dt(x)))
     y = alloc((shares, P, N), torch.float32)
     _check(lib().qe_moe_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), P, E, N, I, shares, _dt(x), _stream()), "moe_down")
-    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, shares, _dt(out), _stream()), "moe_combine")
+    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, shares, _dt(out),
+                                _ptr(top_idx if num_identity else None), E, _ptr(x if num_identity else None), _dt(x), _stream()),
+           "moe_combine")
 
 
 def scaled_add(acc: torch.Tensor, x: torch.Tensor, scale: float, first: bool = False) -> None:
@@ -1439,6 +1467,107 @@ def scaled_add(acc: torch.Tensor, x: torch.Tensor, scale: float, first: bool = F
     _need(acc.shape == x.shape and acc.is_contiguous() and x.is_contiguous(), "scaled_add: two contiguous tensors of one shape")
     _check(lib().qe_scaled_add(_ptr(acc), _dt(acc), _ptr(x), _dt(x), ctypes.c_float(scale), int(bool(first)),
                                ctypes.c_long(acc.numel()), _stream()), "scaled_add")
+
+
+def qk_bias_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, q_bias: Optional[torch.Tensor],
+                          k_bias: Optional[torch.Tensor], eps: float, q_temp, kv_pages: Optional[torch.Tensor],
+                          slot_mapping: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                          write_kv: bool = True) -> None:
+    """Attention whose values are its keys as projected: on the leading (Hq + Hkv) D columns of the stacked projection
+    output ``proj`` (rows may be strided), in place and in float32: the biases are added (float32 [Hq D], [Hkv D];
+    optional); the keys as they then are go to the value plane of ``kv_pages`` [pages, 2, Hkv, page, D]; q and k are
+    divided by their root mean square over a head (no weight); q is multiplied by the temperature of its position p,
+    1 + coef ln(floor((p + 1) / every) + 1) for ``q_temp`` = (coef, every) (None: none); the normed keys go to the key
+    plane."""
+    T = proj.shape[0]
+    Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    _rows(proj, "qk_bias_norm_kv_write: proj")
+    _need(proj.shape[1] >= (Hq + Hkv) * D, "qk_bias_norm_kv_write: proj must hold q and k side by side")
+    _i32(positions, "positions")
+    page_size = 1
+    if write_kv:
+        _need(kv_pages is not None and slot_mapping is not None, "qk_bias_norm_kv_write: cache write without a cache")
+        _need(kv_pages.dtype == proj.dtype and kv_pages.is_contiguous() and kv_pages.dim() == 5
+              and kv_pages.shape[1] == 2 and kv_pages.shape[2] == Hkv and kv_pages.shape[4] == D,
+              "qk_bias_norm_kv_write: kv_pages must be [pages, 2, Hkv, page, D] in proj's dtype")
+        _i32(slot_mapping, "slot_mapping")
+        page_size = kv_pages.shape[3]
+    for b, n in ((q_bias, Hq * D), (k_bias, Hkv * D)):
+        _need(b is None or (b.dtype == torch.float32 and b.shape == (n,) and b.is_contiguous()),
+              "qk_bias_norm_kv_write: biases must be float32 [heads D]")
+    coef, every = (0.0, 0) if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+    _need(q_temp is None or every >= 1, "qk_bias_norm_kv_write: the temperature's step must be positive")
+    _check(lib().qe_qk_bias_norm_kv_write(_ptr(proj), ctypes.c_long(proj.stride(0)), _ptr(positions), _ptr(q_bias), _ptr(k_bias),
+                                          ctypes.c_float(eps), ctypes.c_float(coef), every,
+                                          _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
+                                          T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(proj), _stream()),
+           "qk_bias_norm_kv_write")
+
+
+def stream_conv(resid: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], ctx, out_plain: Optional[torch.Tensor],
+                out_conv: torch.Tensor, write_state: bool = True) -> None:
+    """What a sublayer reads of the float32 residual stream ``resid`` [T, W]: out_plain = resid and out_conv = resid +
+    conv(resid), both rounded once to the compute type, conv a causal convolution over the tokens of each request on
+    each channel, conv(x)[t, c] = sum_j w[c, j] x[t - (taps - 1) + j, c] with w float32 [W, taps].  state float32
+    [slots, taps - 1, W] holds each request's last taps - 1 rows (zeros count for a request without context) and is
+    moved on; None where taps = 1."""
+    T, W = resid.shape
+    taps = w.shape[1]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "stream_conv: resid must be contiguous float32")
+    _need(w.shape == (W, taps) and w.dtype == torch.float32 and w.is_contiguous(), "stream_conv: w must be float32 [W, taps]")
+    if taps > 1:
+        _need(state is not None and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, W),
+              "stream_conv: state must be float32 [slots, taps - 1, W]")
+    for o in (out_plain, out_conv):
+        _need(o is None or (o.shape == (T, W) and o.is_contiguous() and o.dtype == out_conv.dtype), "stream_conv: outputs must be contiguous [T, W]")
+    _check(lib().qe_stream_conv(_ptr(resid), _ptr(w), _ptr(state if taps > 1 else None), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens),
+                                _ptr(ctx.slot_ids), _ptr(out_plain), _ptr(out_conv), int(ctx.num_reqs), int(ctx.max_q_len), W,
+                                taps, int(bool(write_state)), _dt(out_conv), _stream()), "stream_conv")
+
+
+def gated_norm_add(src: torch.Tensor, branch: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
+                   weight: torch.Tensor, eps: float, dst: torch.Tensor, dst_cast: Optional[torch.Tensor] = None) -> None:
+    """A sublayer's way back into the float32 stream with the norm on the sublayer's side:
+    dst[t] = src[t] + rmsnorm(branch[t] * sigmoid(gate[t] + gate_bias)) * weight, float32 arithmetic; ``gate`` None:
+    no gate.  src, dst float32 [T, W] (may be the same tensor); branch and gate [T, W] in float32 or the compute
+    type; gate_bias, weight float32 [W]; ``dst_cast`` [T, W]: dst once more, rounded to its type."""
+    T, W = src.shape
+    _need(src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous()
+          and dst.shape == (T, W), "gated_norm_add: src and dst must be contiguous float32 [T, W]")
+    _need(branch.shape == (T, W) and branch.is_contiguous(), "gated_norm_add: branch must be contiguous [T, W]")
+    _need(weight.dtype == torch.float32 and weight.shape == (W,), "gated_norm_add: weight must be float32 [W]")
+    if gate is not None:
+        _need(gate.shape == (T, W) and gate.is_contiguous(), "gated_norm_add: gate must be contiguous [T, W]")
+        _need(gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.shape == (W,)), "gated_norm_add: gate_bias must be float32 [W]")
+    if dst_cast is not None:
+        _need(dst_cast.shape == (T, W) and dst_cast.is_contiguous(), "gated_norm_add: dst_cast must be contiguous [T, W]")
+    _check(lib().qe_gated_norm_add(_ptr(src), _ptr(branch), _dt(branch), _ptr(gate), _dt(gate) if gate is not None else 0,
+                                   _ptr(gate_bias if gate is not None else None), _ptr(weight), ctypes.c_float(eps), _ptr(dst),
+                                   _ptr(dst_cast), _dt(dst_cast) if dst_cast is not None else 0, T, W, _stream()), "gated_norm_add")
+
+
+def token_side_gate(gate: torch.Tensor, table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(gate[t, j]) * table[token_ids[t], j]: a second embedding's row, gated; float32 arithmetic,
+    rounded once.  gate, out [T, d] and table [V, d] in the compute type."""
+    T, d = gate.shape
+    _i32(token_ids, "token_ids")
+    _need(table.dim() == 2 and table.shape[1] == d and table.is_contiguous() and table.dtype == gate.dtype,
+          "token_side_gate: table must be contiguous [V, d] in gate's dtype")
+    _need(gate.is_contiguous() and out.shape == (T, d) and out.is_contiguous() and out.dtype == gate.dtype,
+          "token_side_gate: gate and out must be contiguous [T, d]")
+    _check(lib().qe_token_side_gate(_ptr(gate), _ptr(table), _ptr(token_ids), _ptr(out), T, d, int(table.shape[0]), _dt(gate),
+                                    _stream()), "token_side_gate")
+
+
+def depth_mix(history: torch.Tensor, weights: torch.Tensor, count: int, out: torch.Tensor) -> None:
+    """out = sum over j < count of weights[j] * history[j]: a weighted sum of the results of the layers so far.
+    history float32 [L, T, W] contiguous, weights float32 [>= count] on the device, out float32 [T, W]; the sum runs in
+    the order of j."""
+    _need(history.dim() == 3 and history.dtype == torch.float32 and history.is_contiguous() and 1 <= count <= history.shape[0],
+          "depth_mix: history must be contiguous float32 [L, T, W] with count <= L")
+    _need(weights.dtype == torch.float32 and weights.numel() >= count and weights.is_contiguous(), "depth_mix: weights must be float32 [count]")
+    _need(out.shape == history.shape[1:] and out.dtype == torch.float32 and out.is_contiguous(), "depth_mix: out must be float32 [T, W]")
+    _check(lib().qe_depth_mix(_ptr(history), _ptr(weights), int(count), _ptr(out), ctypes.c_long(out.numel()), _stream()), "depth_mix")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -11,8 +11,9 @@ from .moe import RoutedExperts
 from .parallel import ParallelMixers
 from .mlp import SwiGLU
 from .block import PreNormBlock
+from .gated_post_norm import GatedPostNormBlock
 
 __all__ = ["Arena", "Block", "FeedForward", "GroupStepView", "Mixer", "Norm", "Part", "PartSpec",
            "PositionEncoding", "StepContext", "register", "NORMS", "POSITION_ENCODINGS", "MIXERS",
            "FEED_FORWARDS", "BLOCKS", "RMSNorm", "NeoxRope", "GQAAttention", "GatedLinearAttention", "DecayedLinearAttention", "LatentAttention", "GatedDeltaRule", "RoutedExperts", "ParallelMixers", "SwiGLU",
-           "PreNormBlock"]
+           "PreNormBlock", "GatedPostNormBlock"]

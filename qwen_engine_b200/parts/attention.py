@@ -19,6 +19,12 @@ Options that other designs use (all off for Qwen3):
 * ``output_gate`` = "sigmoid": the joined heads are multiplied by
   sigmoid(W_g x) before the output projection; W_g rides in the stacked product.
 * no position encoding at all (``position_encoding`` None).
+* ``tied_values``: there is no W_v; the values are the keys as projected (with their bias, before their
+  norm).  The cache's value plane takes the projected keys and its key plane the normed ones, so the
+  attention kernels see an ordinary cache.  Comes with ``qk_bias`` (biases of the q and k projections),
+  a q/k norm without weights (``qk_norm_eps`` is its eps), and
+  ``query_temperature`` = (coef, every): the query at position p is multiplied by
+  1 + coef ln(floor((p + 1) / every) + 1).
 * ``names``: the tensors' names in the checkpoint.
 """
 from __future__ import annotations
@@ -29,11 +35,12 @@ import torch
 
 from .. import ops
 from ..cache.spec import PagedKVSpec
-from ..weights.spec import MATRIX, NORM, WeightSpec
+from ..weights.spec import MATRIX, NORM, VECTOR, WeightSpec
 from .base import Mixer, PartSpec, StepContext, register, step_hint
 
 _NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", out="o_proj.weight",
-              q_norm="q_norm.weight", k_norm="k_norm.weight", gate="g_proj.weight")
+              q_norm="q_norm.weight", k_norm="k_norm.weight", gate="g_proj.weight",
+              q_bias="q_proj.bias", k_bias="k_proj.bias")
 
 
 def _pad_rows(w: torch.Tensor, heads: int, dim: int, padded: int) -> torch.Tensor:
@@ -53,7 +60,8 @@ class GQAAttention(Mixer):
                  scale: float, qk_norm_eps: Optional[float] = None,
                  position_encoding: Optional[PartSpec] = None, window: Optional[int] = None,
                  value_dim: Optional[int] = None, distance_slopes=None, output_gate: Optional[str] = None,
-                 names: Optional[dict] = None):
+                 names: Optional[dict] = None, tied_values: bool = False, qk_bias: bool = False,
+                 query_temperature=None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if output_gate not in (None, "sigmoid"):
@@ -74,14 +82,24 @@ class GQAAttention(Mixer):
         self.q_width = num_heads * self.head_dim
         self.kv_width = num_kv_heads * self.head_dim
         self.output_gate = output_gate
+        self.tied_values = bool(tied_values)
+        self.qk_bias = bool(qk_bias)
+        self.query_temperature = None if query_temperature is None else (float(query_temperature[0]), int(query_temperature[1]))
+        if self.tied_values:
+            if self.value_dim != self.key_dim or self.pos is not None or distance_slopes is not None or window:
+                raise ValueError("values that are the keys: one head size, no rotation, no distance bias, no window")
+            if qk_norm_eps is None:
+                raise ValueError("values that are the keys: the q/k norm's eps is needed")
+        elif self.qk_bias or self.query_temperature is not None:
+            raise ValueError("q/k biases and a query temperature come with values that are the keys")
         self.distance_slopes = None if distance_slopes is None else tuple(float(x) for x in distance_slopes)
         self.names = dict(_NAMES, **(names or {}))
         # the step takes the route of separate operations (one stacked product, norm and cache write, attention, gate,
         # output product) when any of the options above is on
-        self.extended = bool(output_gate or self.distance_slopes is not None or self.value_dim != self.key_dim)
+        self.extended = bool(output_gate or self.distance_slopes is not None or self.value_dim != self.key_dim or self.tied_values)
         self.inner_width = self.q_width
-        self.input_width = self.q_width + 2 * self.kv_width + (self.q_width if output_gate else 0)
-        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.slopes = None
+        self.input_width = self.q_width + (1 if self.tied_values else 2) * self.kv_width + (self.q_width if output_gate else 0)
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.slopes = self.q_bias = self.k_bias = None
 
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
@@ -95,12 +113,16 @@ class GQAAttention(Mixer):
         specs = [
             WeightSpec(prefix + n["q"], (H * self.key_dim, W), MATRIX),
             WeightSpec(prefix + n["k"], (G * self.key_dim, W), MATRIX),
-            WeightSpec(prefix + n["v"], (G * self.value_dim, W), MATRIX),
-            WeightSpec(prefix + n["out"], (W, H * self.value_dim), MATRIX),
         ]
+        if not self.tied_values:
+            specs.append(WeightSpec(prefix + n["v"], (G * self.value_dim, W), MATRIX))
+        specs.append(WeightSpec(prefix + n["out"], (W, H * self.value_dim), MATRIX))
         if self.output_gate:
             specs.append(WeightSpec(prefix + n["gate"], (H * self.value_dim, W), MATRIX))
-        if self.qk_norm_eps is not None:
+        if self.qk_bias:
+            specs += [WeightSpec(prefix + n["q_bias"], (H * self.key_dim,), VECTOR),
+                      WeightSpec(prefix + n["k_bias"], (G * self.key_dim,), VECTOR)]
+        if self.qk_norm_eps is not None and not self.tied_values:
             specs += [WeightSpec(prefix + n["q_norm"], (self.key_dim,), NORM),
                       WeightSpec(prefix + n["k_norm"], (self.key_dim,), NORM)]
         if self.pos is not None:
@@ -111,8 +133,9 @@ class GQAAttention(Mixer):
         n, H, G, D = self.names, self.num_heads, self.num_kv_heads, self.head_dim
         # q, k and v rows stacked (and the gate's behind them): one product gives [T, q_width + 2 kv_width (+ q_width)]
         rows = [_pad_rows(source.get(prefix + n["q"]), H, self.key_dim, D),
-                _pad_rows(source.get(prefix + n["k"]), G, self.key_dim, D),
-                _pad_rows(source.get(prefix + n["v"]), G, self.value_dim, D)]
+                _pad_rows(source.get(prefix + n["k"]), G, self.key_dim, D)]
+        if not self.tied_values:
+            rows.append(_pad_rows(source.get(prefix + n["v"]), G, self.value_dim, D))
         if self.output_gate:
             rows.append(_pad_rows(source.get(prefix + n["gate"]), H, self.value_dim, D))
         self.w_qkv = ops.prepare_matrix(torch.cat(rows, dim=0).to(dtype).to(device))
@@ -120,7 +143,10 @@ class GQAAttention(Mixer):
         if self.value_dim != D:                      # zero columns where the attention's output is padding
             w_o = _pad_rows(w_o.t().contiguous(), H, self.value_dim, D).t()
         self.w_o = ops.prepare_matrix(w_o.to(dtype).to(device))
-        if self.qk_norm_eps is not None:
+        if self.qk_bias:
+            self.q_bias = source.get(prefix + n["q_bias"]).to(torch.float32).to(device).contiguous()
+            self.k_bias = source.get(prefix + n["k_bias"]).to(torch.float32).to(device).contiguous()
+        if self.qk_norm_eps is not None and not self.tied_values:
             def norm_weight(name):
                 w = source.get(prefix + name).to(torch.float32)
                 return torch.nn.functional.pad(w, (0, D - self.key_dim)).to(device).contiguous()
@@ -149,6 +175,17 @@ class GQAAttention(Mixer):
         T = ctx.num_tokens
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         view = ctx.groups[group]
+        if self.tied_values:
+            # q and k lead the rows; the cache's value plane gets the keys as projected, its key plane the normed ones
+            n_qk = self.q_width + self.kv_width
+            ops.qk_bias_norm_kv_write(proj, ctx.positions, self.q_bias, self.k_bias, self.qk_norm_eps, self.query_temperature,
+                                      cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache)
+            attn = ctx.arena.alloc((T, self.q_width), ctx.dtype) if (self.output_gate or scale != 1.0 or not inner.is_contiguous()) else inner
+            ops.paged_attention(proj, cache, view.block_tables, ctx, attn, self.scale, 0, H, Hkv, D)
+            if attn is not inner:
+                ops.head_norm_gate(attn, proj[:, n_qk:n_qk + self.q_width] if self.output_gate else None, None, 0.0, inner, H, D,
+                                   gate_kind=self.output_gate, scale=scale)
+            return
         n_qkv = self.q_width + 2 * self.kv_width
         qkv = proj[:, :n_qkv]
         if self.pos is not None:

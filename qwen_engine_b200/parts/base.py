@@ -217,6 +217,14 @@ class Norm(Part):
                       rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def norm_add(self, ctx: StepContext, src: torch.Tensor, branch: torch.Tensor, dst: torch.Tensor,
+                 gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None,
+                 cast: Optional[torch.Tensor] = None) -> None:
+        """For arrangements that norm a sublayer's result, not its input: dst = src + norm(branch), src and dst rows of
+        the float32 stream (they may be the same).  With ``gate`` the branch is first multiplied by
+        sigmoid(gate + gate_bias); ``cast`` gets dst once more, rounded to its type."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     def rotate(self, ctx: StepContext, q: torch.Tensor, k: torch.Tensor) -> None:
@@ -308,6 +316,11 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
     capturable = True             # False if any of its parts says so: steps of the model are then never graph-captured
+
+    def cache_specs(self) -> list:
+        """Every cache a run of the layer keeps: its mixer's, and behind them whatever the arrangement itself keeps
+        per request (``forward`` gets the caches and groups in this order)."""
+        return self.mixer.cache_specs()
 
     def forward(self, ctx: StepContext, stream, cache: Optional[torch.Tensor], group: Optional[int],
                 write_cache: bool) -> None:

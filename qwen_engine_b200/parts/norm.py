@@ -56,3 +56,6 @@ class RMSNorm(Norm):
     def add_norm_rows(self, ctx: StepContext, resid, delta, rows, out):
         ops.add_rmsnorm_rows(resid, delta, rows, self.weight, self.eps, out)
         return out
+
+    def norm_add(self, ctx: StepContext, src, branch, dst, gate=None, gate_bias=None, cast=None) -> None:
+        ops.gated_norm_add(src, branch, gate, gate_bias, self.weight, self.eps, dst, cast)

@@ -11,10 +11,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .config import BesavikConfig, ConfigError, GanidraConfig, ModelConfig, Qwen3Config, read_config_json
+from .config import BesavikConfig, ConfigError, GanidraConfig, MerudraConfig, ModelConfig, Qwen3Config, read_config_json
 from .models.decoder import DecoderModel, ModelLayout
 from .models.besavik import besavik_layout
 from .models.ganidra import ganidra_layout
+from .models.merudra import merudra_layout
 from .models.qwen3 import qwen3_layout
 
 
@@ -35,6 +36,7 @@ def register_architecture(name: str, config_class: type, layout: Callable[[Any],
 register_architecture("Qwen3ForCausalLM", Qwen3Config, qwen3_layout)
 register_architecture("Ganidra", GanidraConfig, ganidra_layout)
 register_architecture("Besavik", BesavikConfig, besavik_layout)
+register_architecture("Merudra", MerudraConfig, merudra_layout)
 
 
 def architecture_of(raw_config: dict[str, Any]) -> Architecture:

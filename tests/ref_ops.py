@@ -295,10 +295,15 @@ def unit_norm(x, num_heads, head_dim, eps, scale=1.0):
     x.copy_(y.reshape(T, num_heads * head_dim))
 
 
-def delta_rule_scan(q, k, v, g, beta, state, ctx, out, num_heads, num_key_heads, key_dim, value_dim, write_state=True):
+def delta_rule_scan(q, k, v, g, beta, state, ctx, out, num_heads, num_key_heads, key_dim, value_dim, write_state=True,
+                    head_decay=None):
     H, G, dk, dv = num_heads, num_key_heads, key_dim, value_dim
     rep = H // G
     cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
+    gh = None
+    if head_decay is not None:
+        a, rate, bias = head_decay
+        gh = torch.exp(-torch.exp(rate) * torch.nn.functional.softplus(a.to(torch.float32) + bias))      # [T, H]
     for r in range(len(ctx_lens)):
         a, b = cu[r], cu[r + 1]
         if b <= a:
@@ -310,6 +315,8 @@ def delta_rule_scan(q, k, v, g, beta, state, ctx, out, num_heads, num_key_heads,
             vt = v[t].reshape(H, dv)
             if g is not None:
                 S = S * g[t].reshape(H, dk)[:, None, :]
+            if gh is not None:
+                S = S * gh[t][:, None, None]
             bt = torch.sigmoid(beta[t].to(torch.float32))
             u = bt[:, None] * (vt - (S * kt[:, None, :]).sum(dim=-1))
             S = S + u[:, :, None] * kt[:, None, :]
@@ -318,27 +325,115 @@ def delta_rule_scan(q, k, v, g, beta, state, ctx, out, num_heads, num_key_heads,
             state[slots[r]] = S
 
 
-def moe_route(x, w, bias, top_idx, top_w):
+def moe_route(x, w, bias, top_idx, top_w, scoring="softmax_chosen", correction=None):
     z = x.to(torch.float32) @ w.t()
     if bias is not None:
         z = z + bias
+    if scoring == "softmax_all":
+        s = torch.softmax(z, dim=-1)
+        idx = torch.topk(s if correction is None else s + correction, top_idx.shape[1], dim=-1).indices
+        top_idx.copy_(idx.to(torch.int32))
+        top_w.copy_(torch.gather(s, 1, idx))
+        return
     val, idx = torch.topk(z, top_idx.shape[1], dim=-1)
     top_idx.copy_(idx.to(torch.int32))
     top_w.copy_(torch.softmax(val, dim=-1))
 
 
-def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc):
+def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc, num_identity=0):
     T = x.shape[0]
+    E = w_gate_up.shape[0]
     I = w_gate_up.shape[1] // 2
     acc = torch.zeros(T, w_down.shape[1], dtype=torch.float32)
     for t in range(T):
         for j in range(top_idx.shape[1]):
             e = int(top_idx[t, j])
+            if e >= E:                       # an expert that hands its input on
+                assert e < E + num_identity
+                acc[t] += float(top_w[t, j]) * x[t].to(torch.float32)
+                continue
             gu = (x[t:t + 1].to(torch.float32) @ w_gate_up[e].to(torch.float32).t()).to(x.dtype)
             act = torch.empty(1, I, dtype=x.dtype)
             act_mul(gu, act, activation)
             acc[t] += float(top_w[t, j]) * (act.to(torch.float32) @ w_down[e].to(torch.float32).t())[0]
     out.copy_(acc.to(out.dtype))
+
+
+def qk_bias_norm_kv_write(proj, positions, q_bias, k_bias, eps, q_temp, kv_pages, slot_mapping, num_heads, num_kv_heads,
+                          head_dim, write_kv=True):
+    T = proj.shape[0]
+    Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    q = proj[:, :Hq * D].to(torch.float32)
+    k = proj[:, Hq * D:(Hq + Hkv) * D].to(torch.float32)
+    if q_bias is not None:
+        q = (q + q_bias).to(proj.dtype).to(torch.float32)
+    if k_bias is not None:
+        k = (k + k_bias).to(proj.dtype).to(torch.float32)
+    v = k.reshape(T, Hkv, D)
+    q, k = q.reshape(T, Hq, D), k.reshape(T, Hkv, D)
+    q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps)
+    k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps)
+    if q_temp is not None:
+        coef, every = q_temp
+        steps = torch.div(positions.long() + 1, every, rounding_mode="floor").to(torch.float32)
+        q = q * (1.0 + coef * torch.log(steps + 1.0))[:, None, None]
+    proj[:, :Hq * D] = q.reshape(T, Hq * D).to(proj.dtype)
+    proj[:, Hq * D:(Hq + Hkv) * D] = k.reshape(T, Hkv * D).to(proj.dtype)
+    if write_kv:
+        P = kv_pages.shape[3]
+        slots = slot_mapping.long()
+        page, off = slots // P, slots % P
+        kv_pages[page, 0, :, off, :] = k.to(kv_pages.dtype)
+        kv_pages[page, 1, :, off, :] = v.to(kv_pages.dtype)
+
+
+def stream_conv(resid, w, state, ctx, out_plain, out_conv, write_state=True):
+    taps = w.shape[1]
+    hist = taps - 1
+    cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
+    if out_plain is not None:
+        out_plain.copy_(resid.to(out_plain.dtype))
+    for r in range(len(ctx_lens)):
+        a, b = cu[r], cu[r + 1]
+        if b <= a:
+            continue
+        if hist > 0:
+            old = state[slots[r]].clone() if ctx_lens[r] > 0 else torch.zeros_like(state[slots[r]])     # [hist, W]
+        else:
+            old = resid.new_zeros((0, resid.shape[1]))
+        seq = torch.cat([old, resid[a:b]], dim=0)
+        y = torch.zeros(b - a, resid.shape[1], dtype=torch.float32)
+        for j in range(taps):
+            y = y + seq[j:j + b - a] * w[:, j][None, :]
+        out_conv[a:b] = (resid[a:b] + y).to(out_conv.dtype)
+        if write_state and hist > 0:
+            state[slots[r]] = seq[-hist:]
+
+
+def gated_norm_add(src, branch, gate, gate_bias, weight, eps, dst, dst_cast=None):
+    v = branch.to(torch.float32)
+    if gate is not None:
+        z = gate.to(torch.float32)
+        if gate_bias is not None:
+            z = z + gate_bias
+        v = v * torch.sigmoid(z)
+    res = src + _rms(v, weight, eps)
+    dst.copy_(res)
+    if dst_cast is not None:
+        dst_cast.copy_(res.to(dst_cast.dtype))
+
+
+def token_side_gate(gate, table, token_ids, out):
+    g = gate.to(torch.float32)
+    a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    out.copy_((a * table[token_ids.long()].to(torch.float32)).to(out.dtype))
+
+
+def depth_mix(history, weights, count, out):
+    acc = torch.zeros_like(out)
+    for j in range(count):
+        acc = acc + weights[j] * history[j]
+    out.copy_(acc)
 
 
 def scaled_add(acc, x, scale, first=False):
@@ -400,7 +495,7 @@ def copy_pages(cache, pairs):
         cache[:, dst] = cache[:, src].clone()
 
 
-_NAMES = ["latent_prepare", "head_linear", "short_conv", "unit_norm", "delta_rule_scan", "moe_route", "moe_experts",
+_NAMES = ["qk_bias_norm_kv_write", "stream_conv", "gated_norm_add", "token_side_gate", "depth_mix", "latent_prepare", "head_linear", "short_conv", "unit_norm", "delta_rule_scan", "moe_route", "moe_experts",
           "act_mul", "channel_decay", "linear_attention_scan", "head_norm_gate", "scaled_add", "copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
