@@ -147,3 +147,26 @@ def forward(cfg, weights, tokens, return_layers=False):
         mixed.append(x)
     logits = (rms(x, cfg["norm"]["eps"]) * w["final.norm"]) @ w["head"].T
     return (logits, outputs, mixed) if return_layers else logits
+
+
+def read_model_folder(folder: str):
+    """(config.json as a dict, {tensor name: tensor}) of a model folder."""
+    import json
+    import os
+
+    from safetensors import safe_open
+    with open(os.path.join(folder, "config.json"), "r", encoding="utf-8") as f:
+        cfg = json.load(f)
+    w = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt", device="cpu") as f:
+        for name in f.keys():
+            w[name] = f.get_tensor(name)
+    return cfg, w
+
+
+def greedy(cfg, w, prompt, n_new):
+    """The prompt's greedy continuation, token by token over the whole sequence each time."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(torch.argmax(forward(cfg, w, toks)[-1])))
+    return toks[len(prompt):]
