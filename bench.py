@@ -462,7 +462,8 @@ COMPARE_SIZES = {
 _TIMED_OPS = ("embedding", "linear", "linear_swiglu", "linear_swiglu_small", "linear_silu_mul", "linear_qkv_rope", "act_mul",
               "qk_norm_rope_kv_write", "paged_attention", "channel_decay", "linear_attention_scan", "head_norm_gate",
               "add_rmsnorm", "add_rmsnorm_rows", "rope_table", "latent_prepare", "head_linear", "short_conv", "unit_norm",
-              "delta_rule_scan", "moe_route", "moe_experts")
+              "delta_rule_scan", "moe_route", "moe_experts", "qk_bias_norm_kv_write", "stream_conv", "gated_norm_add",
+              "token_side_gate", "depth_mix")
 
 
 def ganidra_config_of(sz: dict) -> dict:
@@ -495,10 +496,26 @@ def besavik_config_of(sz: dict) -> dict:
                 layers=four * (sz["layers"] // 4))
 
 
+def merudra_config_of(sz: dict) -> dict:
+    """A Merudra model at the sizes of ``sz``: attention whose values are its keys twice, the delta mixer with one decay
+    per head, attention again, twice over; behind every mixer eight experts of half the dense feed-forward's width and two
+    that hand their input on, two per token; streams read through convolutions of four taps; a token input of 64 columns
+    per layer."""
+    D = sz["head_dim"]
+    attn = dict(heads=sz["heads"], kv_heads=sz["kv_heads"], dim=D, vdim=D, scale=D ** -0.5, q_temp=dict(coef=0.1, every=512))
+    delta = dict(heads=sz["gla_heads"], kv_heads=max(1, sz["gla_heads"] // 2), dim=sz["gla_dk"], vdim=sz["gla_dv"], conv=4)
+    moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2), router=dict(experts=8, identity=2, top=2))
+    four = [dict(type="attention", mixer=attn, mlp=moe), dict(type="attention", mixer=attn, mlp=moe),
+            dict(type="delta", mixer=delta, mlp=moe), dict(type="attention", mixer=attn, mlp=moe)]
+    return dict(architecture="Merudra", vocab=sz["vocab"], width=sz["width"], norm=dict(eps=1e-6), canon=dict(taps=4),
+                token_side=dict(dim=64), layers=four * (sz["layers"] // 4))
+
+
 def compare_designs(args) -> int:
     """``--compare ganidra``: prefill and decode of a Ganidra model beside a Qwen3 model of equal sizes (random weights,
     bfloat16), and the device time of every class of operation in one eager step of each (CUDA events around every
-    call, the calls of a class added up).  ``--compare besavik``: a Besavik model beside both.  Prints one JSON line."""
+    call, the calls of a class added up).  ``--compare besavik``: a Besavik model beside both.  ``--compare merudra``: a
+    Merudra model beside a Besavik and a Qwen3 model.  Prints one JSON line."""
     import torch
     from qwen_engine_b200 import ops
     from qwen_engine_b200.config import preset_config_dict
@@ -606,17 +623,20 @@ def compare_designs(args) -> int:
         qraw = preset_config_dict(sz["preset"])
         qraw.update(num_hidden_layers=sz["layers"], vocab_size=sz["vocab"])
         out[name] = {"sizes": sz}
-        if args.compare == "besavik":
+        if args.compare == "merudra":
+            out[name]["merudra"] = measure(config_from_dict(merudra_config_of(sz)), "merudra")
+        if args.compare in ("besavik", "merudra"):
             out[name]["besavik"] = measure(config_from_dict(besavik_config_of(sz)), "besavik")
-        out[name]["ganidra"] = measure(config_from_dict(ganidra_config_of(sz)), "ganidra")
+        if args.compare != "merudra":
+            out[name]["ganidra"] = measure(config_from_dict(ganidra_config_of(sz)), "ganidra")
         out[name]["qwen3"] = measure(config_from_dict(qraw), "qwen3")
-        designs = [d for d in ("besavik", "ganidra", "qwen3") if d in out[name]]
+        designs = [d for d in ("merudra", "besavik", "ganidra", "qwen3") if d in out[name]]
         for other in designs[1:]:
             g, q = out[name][designs[0]], out[name][other]
             out[name][f"{designs[0]}_over_{other}"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
                                                       "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
     clocks.stop()
-    title = "Besavik beside Ganidra and Qwen3" if args.compare == "besavik" else "Ganidra beside Qwen3"
+    title = {"besavik": "Besavik beside Ganidra and Qwen3", "merudra": "Merudra beside Besavik and Qwen3"}.get(args.compare, "Ganidra beside Qwen3")
     print(json.dumps({"metric": f"prefill and decode tok/s, {title} at equal sizes", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2",
                       "steps": args.steps, "warmup": args.warmup, "peaks": peaks_src, "sizes": out,
@@ -645,9 +665,9 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel-class timings")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--compare", choices=["ganidra", "besavik"], default=None,
+    ap.add_argument("--compare", choices=["ganidra", "besavik", "merudra"], default=None,
                     help="instead of the default workload: prefill and decode of a Ganidra model beside a Qwen3 model of equal "
-                         "sizes (besavik: a Besavik model beside both), with the device time of every class of operation "
+                         "sizes (besavik: a Besavik model beside both; merudra: a Merudra model beside a Besavik and a Qwen3 model), with the device time of every class of operation "
                          "(one JSON line)")
     ap.add_argument("--compare-size", choices=sorted(COMPARE_SIZES), default=None, help="with --compare: one size only")
     args = ap.parse_args()
