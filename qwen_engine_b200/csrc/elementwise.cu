@@ -583,6 +583,74 @@ __global__ void qk_bias_norm_kv_write_kernel(T* __restrict__ proj, long stride, 
   }
 }
 
+// The same for bfloat16 heads of up to 256 channels in 16-byte pieces (D a multiple of 8, rows and pages on 16-byte
+// boundaries): a lane takes one piece of the head, so a head is one load, and its stores are one or three.
+__global__ void qk_bias_norm_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ proj, long stride, const int* __restrict__ positions,
+                                                    const float* __restrict__ q_bias, const float* __restrict__ k_bias, float eps,
+                                                    float temp_coef, int temp_every, __nv_bfloat16* __restrict__ pages,
+                                                    const int* __restrict__ slot_mapping, int T_tokens, int Hq, int Hkv, int D,
+                                                    int page_size, int write_kv) {
+  pdl_launch_dependents();
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_total = Hq + Hkv;
+  const long item = (long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long)T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int head = (int)(item % heads_total);
+  const bool is_q = head < Hq;
+  const int h = is_q ? head : head - Hq;
+  const bool mine = lane * 8 < D;
+  // what no kernel writes: the bias, the position's temperature, the token's place in the cache
+  float b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = 0.f;
+  const float* bias = is_q ? q_bias : k_bias;
+  if (bias && mine) {
+    const float4 b0 = *reinterpret_cast<const float4*>(bias + (size_t)h * D + lane * 8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias + (size_t)h * D + lane * 8 + 4);
+    b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+  }
+  float temp = 1.f;
+  if (is_q && temp_every > 0) temp = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.f);
+  __nv_bfloat16* key_dst = nullptr;
+  __nv_bfloat16* value_dst = nullptr;
+  if (!is_q && write_kv) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    key_dst = pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + lane * 8;
+    value_dst = pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + lane * 8;
+  }
+  pdl_wait();
+  __nv_bfloat16* x = proj + (size_t)t * stride + (size_t)head * D + lane * 8;
+  float v[8];
+  float ss = 0.f;
+  if (mine) {
+    uint4 raw = *reinterpret_cast<const uint4*>(x);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    __nv_bfloat162 stored[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(p2[i]);
+      stored[i] = __floats2bfloat162_rn(f.x + b[2 * i], f.y + b[2 * i + 1]);      // the projection's output with its bias, as stored
+      const float2 r = __bfloat1622float2(stored[i]);
+      v[2 * i] = bias ? r.x : f.x; v[2 * i + 1] = bias ? r.y : f.y;
+      ss = fmaf(v[2 * i], v[2 * i], ss); ss = fmaf(v[2 * i + 1], v[2 * i + 1], ss);
+    }
+    if (value_dst) *reinterpret_cast<uint4*>(value_dst) = bias ? *reinterpret_cast<const uint4*>(stored) : raw;
+  }
+  ss = warp_sum(ss);
+  const float f = rsqrtf(ss / (float)D + eps) * temp;
+  if (mine) {
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(v[2 * i] * f, v[2 * i + 1] * f);
+    const uint4 out = *reinterpret_cast<const uint4*>(o);
+    *reinterpret_cast<uint4*>(x) = out;
+    if (key_dst) *reinterpret_cast<uint4*>(key_dst) = out;
+  }
+}
+
 extern "C" int qe_qk_bias_norm_kv_write(void* proj, long stride, const int* positions, const float* q_bias, const float* k_bias,
                                         float eps, float temp_coef, int temp_every, void* pages, const int* slot_mapping, int T,
                                         int Hq, int Hkv, int D, int page_size, int write_kv, int dtype, cudaStream_t stream) {
@@ -590,9 +658,18 @@ extern "C" int qe_qk_bias_norm_kv_write(void* proj, long stride, const int* posi
   if (D > QKR_MAX_D) QE_REFUSE("qk_bias_norm_kv_write: head_dim %d is above %d", D, QKR_MAX_D);
   if (write_kv && (!pages || !slot_mapping)) QE_REFUSE("qk_bias_norm_kv_write: cache write without cache");
   if (temp_every < 0) QE_REFUSE("qk_bias_norm_kv_write: the temperature's step %d is negative", temp_every);
-  const int warps = 4;
   const long items = (long)T * (Hq + Hkv);
   if (items > 0x7fffff00L) QE_REFUSE("qk_bias_norm_kv_write: %d tokens x %d heads are too many for one launch", T, Hq + Hkv);
+  if (dtype == QE_DTYPE_BF16 && D % 8 == 0 && D <= 256 && stride % 8 == 0 &&
+      (((uintptr_t)proj | (uintptr_t)pages | (uintptr_t)q_bias | (uintptr_t)k_bias) & 15) == 0) {
+    const int vwarps = 8;
+    qe_launch(qk_bias_norm_kv_write_bf16x8_kernel, dim3((unsigned)((items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0, stream,
+              (__nv_bfloat16*)proj, stride, positions, q_bias, k_bias, eps, temp_coef, temp_every, (__nv_bfloat16*)pages, slot_mapping,
+              T, Hq, Hkv, D, page_size, write_kv);
+    QE_CHECK_LAUNCH("qk_bias_norm_kv_write");
+    return 0;
+  }
+  const int warps = 4;
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * D * sizeof(float);
 #define QKB(TT) qe_launch(qk_bias_norm_kv_write_kernel<TT>, dim3(blocks), dim3(warps * 32), smem, stream, (TT*)proj, stride, \

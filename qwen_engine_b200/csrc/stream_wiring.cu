@@ -12,75 +12,105 @@
 #include <math.h>
 
 #define SW_MAX_TAPS 16
-#define SW_TOKENS 32
+#define SW_TOKENS 16            // tokens of a request a CTA takes: at least as many as a window holds rows of the past
+#define SW_GROUPS 16            // channel groups a CTA takes
 
-// out_plain[t, c] = x[t, c]; out_conv[t, c] = x[t, c] + sum_j w[c, j] x[t - (taps - 1) + j, c].  A thread per channel
-// walks up to SW_TOKENS tokens of one request with the window in registers.  Rows before the step's first come from the
-// request's state (zeros for a request without context).  The CTA of a request's first tokens is the only reader of the
-// state and also its writer.
-template <typename T>
-__global__ void __launch_bounds__(128)
+// out_plain[t, c] = x[t, c]; out_conv[t, c] = x[t, c] + sum_j w[c, j] x[t - (taps - 1) + j, c].  A thread takes one token
+// and CH neighbouring channels (one 16-byte load a row where CH = 4); the rows it shares with its neighbours come from
+// L1/L2.  Rows before the step's first come from the request's state (zeros for a request without context).  The CTA of a
+// request's first tokens is the only reader of the state and, behind a barrier, also its writer (a portion shorter than
+// the window shifts the old rows: they are read before the barrier and written after a second one).
+template <int CH> struct SwVec { float v[CH]; };
+
+template <int CH>
+__device__ __forceinline__ SwVec<CH> sw_ld(const float* p) {
+  SwVec<CH> r;
+  if constexpr (CH == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; }
+  else r.v[0] = p[0];
+  return r;
+}
+template <typename T, int CH>
+__device__ __forceinline__ void sw_st(T* p, const SwVec<CH>& a) {
+  if constexpr (CH == 4 && sizeof(T) == 2) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.v[0], a.v[1]), hi = __floats2bfloat162_rn(a.v[2], a.v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else if constexpr (CH == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+  } else {
+    p[0] = from_f32<T>(a.v[0]);
+  }
+}
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(SW_TOKENS * SW_GROUPS)
 stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ state,
                    const int* __restrict__ cu_q, const int* __restrict__ ctx_lens, const int* __restrict__ slot_ids,
                    T* __restrict__ out_plain, T* __restrict__ out_conv, int C, int taps, int write_state) {
   pdl_launch_dependents();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int grp = threadIdx.x % SW_GROUPS, tok = threadIdx.x / SW_GROUPS;
+  const int c = (blockIdx.x * SW_GROUPS + grp) * CH;
   const int req = blockIdx.y;
-  float wt[SW_MAX_TAPS];
-#pragma unroll
-  for (int j = 0; j < SW_MAX_TAPS; ++j) wt[j] = (c < C && j < taps) ? w[(size_t)c * taps + j] : 0.f;
-  pdl_wait();
-  if (c >= C) return;
-  const int row0 = cu_q[req], n = cu_q[req + 1] - row0;
-  const int t0 = blockIdx.z * SW_TOKENS;
-  if (t0 >= n) return;
-  const int ctx = ctx_lens[req];
   const int hist = taps - 1;
-  float* st = hist > 0 ? state + (size_t)slot_ids[req] * hist * C + c : nullptr;      // [hist][C]: the oldest row first
-  auto input = [&](int t) -> float {
-    if (t >= 0) return x[(size_t)(row0 + t) * C + c];
-    return (ctx > 0 && hist + t >= 0) ? st[(size_t)(hist + t) * C] : 0.f;
-  };
-  float win[SW_MAX_TAPS];                                          // win[j]: the row taps - 1 - j tokens back
+  const bool in_c = c < C;
+  // the channels' weights depend on nothing a kernel writes
+  float wt[CH][SW_MAX_TAPS];
 #pragma unroll
-  for (int j = 0; j < SW_MAX_TAPS; ++j) win[j] = (j < hist) ? input(t0 - hist + j) : 0.f;
-  float old_tail[SW_MAX_TAPS];
-  const bool keeper = blockIdx.z == 0 && write_state && hist > 0;
-  if (keeper) {
+  for (int e = 0; e < CH; ++e)
 #pragma unroll
-    for (int j = 0; j < SW_MAX_TAPS; ++j) old_tail[j] = (j < hist) ? win[j] : 0.f;    // the state as it was (zeros without context)
-  }
-  const int t1 = min(n, t0 + SW_TOKENS);
-  for (int t = t0; t < t1; ++t) {
-    const size_t at = (size_t)(row0 + t) * C + c;
-    const float cur = x[at];
-    float acc = 0.f;
+    for (int j = 0; j < SW_MAX_TAPS; ++j) wt[e][j] = (in_c && j < taps) ? w[(size_t)(c + e) * taps + j] : 0.f;
+  pdl_wait();
+  const int row0 = cu_q[req], n = cu_q[req + 1] - row0;
+  if (blockIdx.z * SW_TOKENS >= n) return;            // (the whole CTA)
+  const int t = blockIdx.z * SW_TOKENS + tok;
+  const int ctx = ctx_lens[req];
+  float* st = (hist > 0 && in_c) ? state + (size_t)slot_ids[req] * hist * C + c : nullptr;      // [hist][C]: the oldest row first
+  if (in_c && t < n) {
+    SwVec<CH> acc;
 #pragma unroll
-    for (int j = 0; j < SW_MAX_TAPS; ++j) {
-      if (j < hist) acc = fmaf(wt[j], win[j], acc);
-    }
-    acc = fmaf(wt[hist], cur, acc);
-    if (out_plain) out_plain[at] = from_f32<T>(cur);
-    out_conv[at] = from_f32<T>(cur + acc);
+    for (int e = 0; e < CH; ++e) acc.v[e] = 0.f;
+    // taps in the order of time: the oldest row first, the token itself last
 #pragma unroll
-    for (int j = 0; j < SW_MAX_TAPS - 1; ++j) win[j] = win[j + 1];
-    if (hist > 0) {
+    for (int j = 0; j < SW_MAX_TAPS - 1; ++j) {
+      if (j < hist) {
+        const int back = t - hist + j;
+        SwVec<CH> r;
+        if (back >= 0) r = sw_ld<CH>(x + (size_t)(row0 + back) * C + c);
+        else if (ctx > 0 && hist + back >= 0) r = sw_ld<CH>(st + (size_t)(hist + back) * C);
+        else {
 #pragma unroll
-      for (int j = 0; j < SW_MAX_TAPS; ++j) if (j == hist - 1) win[j] = cur;
-    }
-  }
-  if (keeper) {
-    for (int j = 0; j < hist; ++j) {
-      const int t = n - hist + j;                                   // the step's row that lands in place j
-      float v;
-      if (t >= 0) v = x[(size_t)(row0 + t) * C + c];
-      else {
-        v = 0.f;
+          for (int e = 0; e < CH; ++e) r.v[e] = 0.f;
+        }
 #pragma unroll
-        for (int i = 0; i < SW_MAX_TAPS; ++i) if (i == hist + t) v = old_tail[i];
+        for (int e = 0; e < CH; ++e) acc.v[e] = fmaf(wt[e][j], r.v[e], acc.v[e]);
       }
-      st[(size_t)j * C] = v;
     }
+    const size_t at = (size_t)(row0 + t) * C + c;
+    const SwVec<CH> cur = sw_ld<CH>(x + at);
+#pragma unroll
+    for (int e = 0; e < CH; ++e) {
+      float last = 0.f;
+#pragma unroll
+      for (int j = 0; j < SW_MAX_TAPS; ++j) if (j == hist) last = wt[e][j];
+      acc.v[e] = cur.v[e] + fmaf(last, cur.v[e], acc.v[e]);
+    }
+    if (out_plain) sw_st<T, CH>(out_plain + at, cur);
+    sw_st<T, CH>(out_conv + at, acc);
+  }
+  if (blockIdx.z == 0 && write_state && hist > 0) {
+    // the last taps - 1 rows: from this step's rows and, where they are fewer, from the state as it was
+    const int j = tok;                                // thread (tok, grp) moves row j of the state
+    SwVec<CH> v;
+#pragma unroll
+    for (int e = 0; e < CH; ++e) v.v[e] = 0.f;
+    const int from = n - hist + j;                    // the step's row that lands in place j
+    if (in_c && j < hist) {
+      if (from >= 0) v = sw_ld<CH>(x + (size_t)(row0 + from) * C + c);
+      else if (ctx > 0) v = sw_ld<CH>(st + (size_t)(hist + from) * C);
+    }
+    __syncthreads();                                  // every read of the old rows is done
+    if (in_c && j < hist) sw_st<float, CH>(st + (size_t)j * C, v);
   }
 }
 
@@ -91,12 +121,14 @@ extern "C" int qe_stream_conv(const float* x, const float* w, float* state, cons
   if (taps < 1 || taps > SW_MAX_TAPS) QE_REFUSE("stream_conv: %d taps are outside 1..%d", taps, SW_MAX_TAPS);
   if (taps > 1 && !state) QE_REFUSE("stream_conv: %d taps need a state", taps);
   if (R > 65535) QE_REFUSE("stream_conv: %d requests", R);
-  dim3 grid((C + 127) / 128, R, (max_q_len + SW_TOKENS - 1) / SW_TOKENS);
+  const bool vec = C % 4 == 0 && (((uintptr_t)x | (uintptr_t)state | (uintptr_t)out_plain | (uintptr_t)out_conv) & 15) == 0;
+  const int per = vec ? 4 : 1;
+  dim3 grid(((C + per - 1) / per + SW_GROUPS - 1) / SW_GROUPS, R, (max_q_len + SW_TOKENS - 1) / SW_TOKENS);
   if (grid.z > 65535) QE_REFUSE("stream_conv: a portion of %d tokens is too long", max_q_len);
-#define SCL(TT) qe_launch(stream_conv_kernel<TT>, grid, dim3(128), 0, stream, x, w, state, cu_q, ctx_lens, slot_ids, \
-                          (TT*)out_plain, (TT*)out_conv, C, taps, write_state)
-  if (dtype == QE_DTYPE_F32) SCL(float);
-  else if (dtype == QE_DTYPE_BF16) SCL(__nv_bfloat16);
+#define SCL(TT, CH) qe_launch(stream_conv_kernel<TT, CH>, grid, dim3(SW_TOKENS * SW_GROUPS), 0, stream, x, w, state, cu_q, ctx_lens, \
+                              slot_ids, (TT*)out_plain, (TT*)out_conv, C, taps, write_state)
+  if (dtype == QE_DTYPE_F32) { if (vec) SCL(float, 4); else SCL(float, 1); }
+  else if (dtype == QE_DTYPE_BF16) { if (vec) SCL(__nv_bfloat16, 4); else SCL(__nv_bfloat16, 1); }
   else QE_REFUSE("stream_conv: unknown dtype %d", dtype);
 #undef SCL
   QE_CHECK_LAUNCH("stream_conv");
@@ -105,53 +137,136 @@ extern "C" int qe_stream_conv(const float* x, const float* w, float* state, cons
 
 // ---------------------------------------------------------------------------------------------------------
 // dst[t] = src[t] + v / sqrt(mean(v^2) + eps) * w with v = branch[t] * sigmoid(gate[t] + bias) (gate null: v = branch[t]).
-// A CTA per row; the row's v stays in shared memory between the sum and the scaling.
+// A CTA per row; the row's v stays in shared memory between the sum and the scaling.  With `history` (float32
+// [count, T, W], dst being its last entry's row) the row also leaves as the weighted sum over the entries,
+// mixed[t] = sum_j mix_w[j] history[j][t], in the order of j: the layers' results so far, this one included.
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sw_load(const void* p, int dtype, size_t at) {
   return dtype == QE_DTYPE_F32 ? ((const float*)p)[at] : __bfloat162float(((const __nv_bfloat16*)p)[at]);
 }
 
+struct GnaArgs {
+  const float* src; const void* branch; int branch_dtype; const void* gate; int gate_dtype; const float* gate_bias;
+  const float* w; float eps; float* dst; void* dst_cast; int cast_dtype; int W;
+  const float* history; const float* mix_w; int count; long entry_stride; float* mixed;
+};
+
 __global__ void __launch_bounds__(256)
-gated_norm_add_kernel(const float* __restrict__ src, const void* __restrict__ branch, int branch_dtype,
-                      const void* __restrict__ gate, int gate_dtype, const float* __restrict__ gate_bias,
-                      const float* __restrict__ w, float eps, float* __restrict__ dst, void* __restrict__ dst_cast,
-                      int cast_dtype, int W) {
+gated_norm_add_kernel(GnaArgs A) {
   extern __shared__ float sw_row[];                 // [W], then 33 floats for the sum
+  const int W = A.W;
   float* scratch = sw_row + W;
   pdl_launch_dependents();
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * W;
   float ss = 0.f;
   for (int d = threadIdx.x; d < W; d += blockDim.x) {
-    float v = sw_load(branch, branch_dtype, base + d);
-    if (gate) {
-      const float z = sw_load(gate, gate_dtype, base + d) + (gate_bias ? gate_bias[d] : 0.f);
+    float v = sw_load(A.branch, A.branch_dtype, base + d);
+    if (A.gate) {
+      const float z = sw_load(A.gate, A.gate_dtype, base + d) + (A.gate_bias ? A.gate_bias[d] : 0.f);
       v *= 1.f / (1.f + expf(-z));
     }
     sw_row[d] = v;
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
-  const float rstd = rsqrtf(ss / (float)W + eps);
+  const float rstd = rsqrtf(ss / (float)W + A.eps);
   for (int d = threadIdx.x; d < W; d += blockDim.x) {
-    const float o = src[base + d] + sw_row[d] * rstd * w[d];
-    dst[base + d] = o;
-    if (dst_cast) {
-      if (cast_dtype == QE_DTYPE_F32) ((float*)dst_cast)[base + d] = o;
-      else ((__nv_bfloat16*)dst_cast)[base + d] = __float2bfloat16_rn(o);
+    const float o = A.src[base + d] + sw_row[d] * rstd * A.w[d];
+    A.dst[base + d] = o;
+    if (A.dst_cast) {
+      if (A.cast_dtype == QE_DTYPE_F32) ((float*)A.dst_cast)[base + d] = o;
+      else ((__nv_bfloat16*)A.dst_cast)[base + d] = __float2bfloat16_rn(o);
+    }
+    if (A.history) {
+      float acc = 0.f;
+      for (int j = 0; j + 1 < A.count; ++j) acc = fmaf(A.mix_w[j], A.history[(size_t)j * A.entry_stride + base + d], acc);
+      A.mixed[base + d] = fmaf(A.mix_w[A.count - 1], o, acc);
+    }
+  }
+}
+
+// The same for bfloat16 branch, gate and copy on 8-byte boundaries with W a multiple of 4: four channels a thread and turn.
+__global__ void __launch_bounds__(256)
+gated_norm_add_bf16x4_kernel(GnaArgs A) {
+  extern __shared__ float sw_row[];
+  const int W4 = A.W >> 2;
+  float* scratch = sw_row + A.W;
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base4 = (size_t)blockIdx.x * W4;
+  const uint2* br = reinterpret_cast<const uint2*>(A.branch) + base4;
+  const uint2* gt = A.gate ? reinterpret_cast<const uint2*>(A.gate) + base4 : nullptr;
+  const float4* gb = reinterpret_cast<const float4*>(A.gate_bias);
+  float4* row4 = reinterpret_cast<float4*>(sw_row);
+  auto unpack = [](uint2 u) {
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+  };
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < W4; d += blockDim.x) {
+    float4 v = unpack(br[d]);
+    if (gt) {
+      float4 z = unpack(gt[d]);
+      if (gb) { const float4 bb = gb[d]; z.x += bb.x; z.y += bb.y; z.z += bb.z; z.w += bb.w; }
+      v.x *= 1.f / (1.f + expf(-z.x)); v.y *= 1.f / (1.f + expf(-z.y)); v.z *= 1.f / (1.f + expf(-z.z)); v.w *= 1.f / (1.f + expf(-z.w));
+    }
+    row4[d] = v;
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)A.W + A.eps);
+  const float4* src4 = reinterpret_cast<const float4*>(A.src) + base4;
+  const float4* w4 = reinterpret_cast<const float4*>(A.w);
+  float4* dst4 = reinterpret_cast<float4*>(A.dst) + base4;
+  uint2* cast = A.dst_cast ? reinterpret_cast<uint2*>(A.dst_cast) + base4 : nullptr;
+  const long stride4 = A.entry_stride >> 2;
+  for (int d = threadIdx.x; d < W4; d += blockDim.x) {
+    const float4 s4 = src4[d], v = row4[d], ww = w4[d];
+    float4 o;
+    o.x = s4.x + v.x * rstd * ww.x; o.y = s4.y + v.y * rstd * ww.y; o.z = s4.z + v.z * rstd * ww.z; o.w = s4.w + v.w * rstd * ww.w;
+    dst4[d] = o;
+    if (cast) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+      uint2 u;
+      u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+      cast[d] = u;
+    }
+    if (A.history) {
+      const float4* h4 = reinterpret_cast<const float4*>(A.history) + base4 + d;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j + 1 < A.count; ++j) {
+        const float4 hv = h4[(size_t)j * stride4];
+        const float a = A.mix_w[j];
+        acc.x = fmaf(a, hv.x, acc.x); acc.y = fmaf(a, hv.y, acc.y); acc.z = fmaf(a, hv.z, acc.z); acc.w = fmaf(a, hv.w, acc.w);
+      }
+      const float a = A.mix_w[A.count - 1];
+      acc.x = fmaf(a, o.x, acc.x); acc.y = fmaf(a, o.y, acc.y); acc.z = fmaf(a, o.z, acc.z); acc.w = fmaf(a, o.w, acc.w);
+      reinterpret_cast<float4*>(A.mixed)[base4 + d] = acc;
     }
   }
 }
 
 extern "C" int qe_gated_norm_add(const float* src, const void* branch, int branch_dtype, const void* gate, int gate_dtype,
                                  const float* gate_bias, const float* w, float eps, float* dst, void* dst_cast, int cast_dtype,
-                                 int T, int W, cudaStream_t stream) {
+                                 int T, int W, const float* history, const float* mix_w, int count, float* mixed,
+                                 cudaStream_t stream) {
   if (T <= 0 || W <= 0) return 0;
   const size_t smem = ((size_t)W + 33) * sizeof(float);
   if (smem > 48 * 1024) QE_REFUSE("gated_norm_add: a row of %d channels does not fit shared memory", W);
+  if (history && (count < 1 || !mix_w || !mixed || dst != history + (size_t)(count - 1) * T * W))
+    QE_REFUSE("gated_norm_add: the weighted sum needs its weights, its output and dst as the last of %d entries", count);
+  GnaArgs A{src, branch, branch_dtype, gate, gate_dtype, gate_bias, w, eps, dst, dst_cast, cast_dtype, W,
+            history, mix_w, count, (long)T * W, mixed};
   const int threads = W >= 1024 ? 256 : W >= 256 ? 128 : 64;
-  qe_launch(gated_norm_add_kernel, dim3(T), dim3(threads), smem, stream, src, branch, branch_dtype, gate, gate_dtype, gate_bias, w,
-            eps, dst, dst_cast, cast_dtype, W);
+  const uintptr_t all = (uintptr_t)src | (uintptr_t)dst | (uintptr_t)w | (uintptr_t)gate_bias | (uintptr_t)history | (uintptr_t)mixed;
+  const uintptr_t half = (uintptr_t)branch | (uintptr_t)gate | (uintptr_t)dst_cast;
+  if (W % 4 == 0 && branch_dtype == QE_DTYPE_BF16 && (!gate || gate_dtype == QE_DTYPE_BF16) && (!dst_cast || cast_dtype == QE_DTYPE_BF16) &&
+      (all & 15) == 0 && (half & 7) == 0)
+    qe_launch(gated_norm_add_bf16x4_kernel, dim3(T), dim3(W >= 2048 ? 256 : W >= 512 ? 128 : 64), smem, stream, A);
+  else
+    qe_launch(gated_norm_add_kernel, dim3(T), dim3(threads), smem, stream, A);
   QE_CHECK_LAUNCH("gated_norm_add");
   return 0;
 }

@@ -1526,11 +1526,14 @@ def stream_conv(resid: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tens
 
 
 def gated_norm_add(src: torch.Tensor, branch: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
-                   weight: torch.Tensor, eps: float, dst: torch.Tensor, dst_cast: Optional[torch.Tensor] = None) -> None:
+                   weight: torch.Tensor, eps: float, dst: torch.Tensor, dst_cast: Optional[torch.Tensor] = None,
+                   depth_mix=None) -> None:
     """A sublayer's way back into the float32 stream with the norm on the sublayer's side:
     dst[t] = src[t] + rmsnorm(branch[t] * sigmoid(gate[t] + gate_bias)) * weight, float32 arithmetic; ``gate`` None:
     no gate.  src, dst float32 [T, W] (may be the same tensor); branch and gate [T, W] in float32 or the compute
-    type; gate_bias, weight float32 [W]; ``dst_cast`` [T, W]: dst once more, rounded to its type."""
+    type; gate_bias, weight float32 [W]; ``dst_cast`` [T, W]: dst once more, rounded to its type.
+    ``depth_mix`` = (history, weights, count, mixed): dst is entry count - 1 of history (float32 [L, T, W]), and the
+    kernel also leaves mixed = sum over j < count of weights[j] * history[j] (as ``depth_mix`` alone would)."""
     T, W = src.shape
     _need(src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous()
           and dst.shape == (T, W), "gated_norm_add: src and dst must be contiguous float32 [T, W]")
@@ -1541,9 +1544,19 @@ def gated_norm_add(src: torch.Tensor, branch: torch.Tensor, gate: Optional[torch
         _need(gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.shape == (W,)), "gated_norm_add: gate_bias must be float32 [W]")
     if dst_cast is not None:
         _need(dst_cast.shape == (T, W) and dst_cast.is_contiguous(), "gated_norm_add: dst_cast must be contiguous [T, W]")
+    history = mix_w = mixed = None
+    count = 0
+    if depth_mix is not None:
+        history, mix_w, count, mixed = depth_mix
+        _need(history.dim() == 3 and history.dtype == torch.float32 and history.is_contiguous() and tuple(history.shape[1:]) == (T, W)
+              and 1 <= count <= history.shape[0] and dst.data_ptr() == history[count - 1].data_ptr(),
+              "gated_norm_add: dst must be the last of the entries of history [L, T, W] that the sum runs over")
+        _need(mix_w.dtype == torch.float32 and mix_w.numel() >= count and mix_w.is_contiguous(), "gated_norm_add: the sum's weights must be float32 [count]")
+        _need(mixed.shape == (T, W) and mixed.dtype == torch.float32 and mixed.is_contiguous(), "gated_norm_add: mixed must be float32 [T, W]")
     _check(lib().qe_gated_norm_add(_ptr(src), _ptr(branch), _dt(branch), _ptr(gate), _dt(gate) if gate is not None else 0,
                                    _ptr(gate_bias if gate is not None else None), _ptr(weight), ctypes.c_float(eps), _ptr(dst),
-                                   _ptr(dst_cast), _dt(dst_cast) if dst_cast is not None else 0, T, W, _stream()), "gated_norm_add")
+                                   _ptr(dst_cast), _dt(dst_cast) if dst_cast is not None else 0, T, W,
+                                   _ptr(history), _ptr(mix_w), int(count), _ptr(mixed), _stream()), "gated_norm_add")
 
 
 def token_side_gate(gate: torch.Tensor, table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -> None:

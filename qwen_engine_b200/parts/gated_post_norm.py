@@ -156,13 +156,18 @@ class GatedPostNormBlock(Block):
             ops.token_side_gate(side_gate, self.side_table, ctx.token_ids, gated)
             side = ctx.arena.alloc((T, W), ctx.dtype)
             ops.linear(gated, self.w_side_proj, side)
-            ops.gated_norm_add(y, side, None, None, self.side_norm_w, self.token_side["eps"], y)
         if self.depth_mix:
             if history is None:
                 raise RuntimeError("gated_post_norm: a weighted sum over the runs' results needs a model that keeps them")
             if history.run + 2 != self.depth_mix:
                 raise RuntimeError(f"gated_post_norm: run {history.run} sums {history.run + 2} results, the layer has {self.depth_mix} weights")
-            ops.depth_mix(history.results, self.depth_w, self.depth_mix, history.mixed)
+        mix = (history.results, self.depth_w, self.depth_mix, history.mixed) if self.depth_mix else None
+        if self.token_side:
+            # the layer's last add also forms the weighted sum over the results so far
+            ops.gated_norm_add(y, side, None, None, self.side_norm_w, self.token_side["eps"], y, depth_mix=mix)
+        elif mix is not None:
+            ops.depth_mix(*mix)
+        if mix is not None:
             stream.resid = history.mixed
         elif history is not None:
             stream.resid = y

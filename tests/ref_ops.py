@@ -410,7 +410,7 @@ def stream_conv(resid, w, state, ctx, out_plain, out_conv, write_state=True):
             state[slots[r]] = seq[-hist:]
 
 
-def gated_norm_add(src, branch, gate, gate_bias, weight, eps, dst, dst_cast=None):
+def gated_norm_add(src, branch, gate, gate_bias, weight, eps, dst, dst_cast=None, depth_mix=None):
     v = branch.to(torch.float32)
     if gate is not None:
         z = gate.to(torch.float32)
@@ -421,6 +421,10 @@ def gated_norm_add(src, branch, gate, gate_bias, weight, eps, dst, dst_cast=None
     dst.copy_(res)
     if dst_cast is not None:
         dst_cast.copy_(res.to(dst_cast.dtype))
+    if depth_mix is not None:
+        history, weights, count, mixed = depth_mix
+        assert dst.data_ptr() == history[count - 1].data_ptr()
+        globals()["depth_mix"](history, weights, count, mixed)
 
 
 def token_side_gate(gate, table, token_ids, out):

@@ -138,6 +138,27 @@ def test_gated_norm_add(ops, dtype, T, W, gated):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("L,T,W", [(1, 3, 40), (4, 9, 256), (7, 33, 97), (3, 70, 1024)])
+def test_the_last_add_of_a_layer_also_forms_the_weighted_sum(ops, dtype, L, T, W):
+    """The add into entry L of the layers' results, and the weighted sum over entries 0 .. L in the same launch: as the
+    add alone followed by the sum alone, to the bit."""
+    g = torch.Generator().manual_seed(L + T + W)
+    hist = torch.randn(L + 2, T, W, generator=g).to(DEV)
+    branch = torch.randn(T, W, generator=g).to(dtype).to(DEV)
+    weight = (1.0 + 0.3 * torch.randn(W, generator=g)).to(DEV)
+    wts = torch.randn(L + 1, generator=g).to(DEV)
+    apart = hist.clone()
+    ops.gated_norm_add(apart[L], branch, None, None, weight, 1e-6, apart[L])
+    want = torch.empty(T, W, dtype=F32, device=DEV)
+    ops.depth_mix(apart, wts, L + 1, want)
+    mixed = torch.empty(T, W, dtype=F32, device=DEV)
+    ops.gated_norm_add(hist[L], branch, None, None, weight, 1e-6, hist[L], depth_mix=(hist, wts, L + 1, mixed))
+    assert torch.equal(hist, apart) and torch.equal(mixed, want)
+    ref = sum(wts[j].double().cpu() * apart[j].double().cpu() for j in range(L + 1))
+    _close(mixed, ref, F32, "sum", tol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,d,V", [(1, 3, 7), (40, 24, 100), (300, 64, 50)])
 def test_token_side_gate(ops, dtype, T, d, V):
     g = torch.Generator().manual_seed(T + d)
@@ -411,6 +432,27 @@ def test_experts_among_which_some_hand_their_input_on(ops, dtype, T, W, I, E, n_
 def test_replay_against_the_plain_model(folders, dtype, name):
     folder = folders[name]
     mh.replay_cases(lambda n: mh.make_replayer(folder, name, dtype, n, poison=1.0e4), folder, name, dtype, f"{name}")
+
+
+@pytest.mark.parametrize("name", ["m-a", "m-d"])
+def test_bfloat16_rows_do_not_depend_on_the_schedule(folders, name):
+    """In bfloat16 a row is judged loosely against the plain model; against the engine's own rows of the whole prompt the
+    rows of a mixed schedule (portions beside single tokens, slots and pages used again) are judged tightly."""
+    from helpers import live_tokens_needed, mixed_steps
+    folder = folders[name]
+    V = mh.vocab_of(name)
+    reqs = {f"m{i}": random_tokens(V, n, 60 + i) for i, n in enumerate([40, 64, 23, 90, 17, 55])}
+    steps = mixed_steps(reqs, seed=11)
+    got = run_steps(mh.make_replayer(folder, name, BF16, live_tokens_needed(steps, 64), poison=1.0e4), steps)
+    for rid, toks in reqs.items():
+        whole = run_steps(mh.make_replayer(folder, name, BF16, 128),
+                          [{"entries": [{"id": "a", "tokens": toks, "want": list(range(len(toks)))}], "end": ["a"]}])["a"]
+        idx = sorted(got[rid])
+        a, b = torch.stack([got[rid][i] for i in idx]).double(), torch.stack([whole[i] for i in idx]).double()
+        d = a - b
+        d = d - d.mean(dim=-1, keepdim=True)
+        err = d.pow(2).mean(dim=-1).sqrt() / (b - b.mean(dim=-1, keepdim=True)).pow(2).mean(dim=-1).sqrt()
+        assert float(err.max()) < 0.1, f"{name} {rid}: position {idx[int(err.argmax())]} differs by {float(err.max()):.3f}"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
