@@ -96,8 +96,24 @@ def plain_logits(folder: str, tokens) -> torch.Tensor:
     key = (folder, tuple(tokens))
     if key not in _plain:
         cfg, w = plain_model(folder)
-        _plain[key] = plain_merudra.forward(cfg, w, list(tokens)).to(torch.float32)
+        margins: list = []
+        _plain[key] = plain_merudra.forward(cfg, w, list(tokens), margins=margins).to(torch.float32)
+        _plain[("margin",) + key] = torch.stack(margins).min(dim=0).values if margins else torch.full((len(tokens),), float("inf"))
     return _plain[key]
+
+
+CLOSE_CALL = 0.02
+
+
+def settled_positions(folder: str, tokens, dtype) -> set:
+    """The positions at which no router of the plain model makes a close call (the last chosen expert beats the first one
+    left out by less than CLOSE_CALL): bfloat16 rounding may decide such a call the other way, and then the row is another
+    expert's, so in bfloat16 rows are judged at the other positions only.  In float32 every position counts."""
+    plain_logits(folder, tokens)
+    m = _plain[("margin", folder, tuple(tokens))]
+    if dtype == torch.float32:
+        return set(range(len(tokens)))
+    return {i for i in range(len(tokens)) if float(m[i]) >= CLOSE_CALL}
 
 
 def vocab_of(name: str) -> int:
@@ -119,7 +135,11 @@ def check_requests(got, folder, requests, dtype, what):
     for rid, toks in requests.items():
         want = plain_logits(folder, toks)
         rows = got[rid]
-        idx = sorted(rows)
+        settled = settled_positions(folder, toks, dtype)
+        idx = [i for i in sorted(rows) if i in settled]
+        assert len(rows) < 10 or len(idx) >= 0.8 * len(rows), f"{what} {rid}: too many close calls to judge"
+        if not idx:
+            continue
         assert_close_rows(torch.stack([rows[i] for i in idx]), want[idx], dtype, f"{what} {rid} (positions {idx[0]}..)")
 
 

@@ -95,13 +95,17 @@ def head_decayed_delta(h, w, p, m, eps):
     return o @ w[p + "o"].T
 
 
-def routed_experts(h, w, p, mlp):
+def routed_experts(h, w, p, mlp, margins=None):
     """Softmax over all router outputs; the `top` largest of score + correction are chosen; the weights are the chosen
-    scores as they are.  The last `identity` router outputs stand for experts that hand the input on."""
+    scores as they are.  The last `identity` router outputs stand for experts that hand the input on.  ``margins`` (a list)
+    gets, per token, by how much the last chosen expert's choice score beats the first one left out."""
     r = mlp["router"]
     E, n_id, top = r["experts"], r["identity"], r["top"]
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)
     choice = s + w[p + "correction"]
+    if margins is not None:
+        ranked = torch.sort(choice, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < choice.shape[1] else torch.full((h.shape[0],), math.inf, dtype=F64))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in torch.topk(choice[t], top).indices.tolist():
@@ -121,7 +125,7 @@ def token_side_input(x, tokens, w, prefix, layer, dim, eps):
     return rms(y, eps) * w[prefix + "side.norm"]
 
 
-def layer(x, tokens, w, i, spec, cfg):
+def layer(x, tokens, w, i, spec, cfg, margins=None):
     """One layer without the depth average: both gated, convolved, post-normed sublayers and the token input."""
     p, eps = f"l{i}.", cfg["norm"]["eps"]
     h = x + causal_conv(x, w[p + "canon1"])
@@ -130,19 +134,19 @@ def layer(x, tokens, w, i, spec, cfg):
     x = x + rms(y, eps) * w[p + "norm1"]
     if spec.get("mlp") is not None:
         h = x + causal_conv(x, w[p + "canon2"])
-        y = routed_experts(h, w, p + "mlp.", spec["mlp"]) * torch.sigmoid(x @ w[p + "rg2"].T + w[p + "rg2.b"])
+        y = routed_experts(h, w, p + "mlp.", spec["mlp"], margins) * torch.sigmoid(x @ w[p + "rg2"].T + w[p + "rg2.b"])
         x = x + rms(y, eps) * w[p + "norm2"]
     return x + token_side_input(x, tokens, w, p, i, cfg["token_side"]["dim"], eps)
 
 
-def forward(cfg, weights, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence, float64."""
+def forward(cfg, weights, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one sequence, float64.  ``margins`` (a list) gets every routed layer's margins."""
     w = {k: v.to(F64) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = w["embed"][tokens]
     outputs, mixed = [x], []
     for i, spec in enumerate(cfg["layers"]):
-        outputs.append(layer(x, tokens, w, i, spec, cfg))
+        outputs.append(layer(x, tokens, w, i, spec, cfg, margins))
         x = sum(w[f"l{i}.dwa"][j] * outputs[j] for j in range(i + 2))          # the depth average
         mixed.append(x)
     logits = (rms(x, cfg["norm"]["eps"]) * w["final.norm"]) @ w["head"].T
