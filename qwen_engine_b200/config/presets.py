@@ -68,6 +68,19 @@ PRESETS: dict[str, dict[str, Any]] = {
                             dict(type="channel_delta", mixer=dict(heads=4, kv_heads=2, dim=16, vdim=32, conv=4, rank=8),
                                  mlp=dict(kind="moe", expert=dict(ff=64, limit=2.0), router=dict(experts=4, top=2)))]),
         init=dict(seed=7, std=0.08, norm_std=0.1, block_size=16)),
+    # a small model of the Merudra design: attention whose values are its keys, the delta rule with one decay per head,
+    # experts scored over all of them with two that hand their input on; the stream read through convolutions of 3 taps
+    "merudra-tiny": dict(
+        config=dict(architecture="Merudra", vocab=320, width=128, norm=dict(eps=1e-6), canon=dict(taps=3), token_side=dict(dim=16),
+                    layers=[dict(type="attention",
+                                 mixer=dict(heads=4, kv_heads=2, dim=32, vdim=32, scale=0.18, q_temp=dict(coef=0.3, every=16)),
+                                 mlp=dict(kind="moe", expert=dict(ff=64), router=dict(experts=4, identity=2, top=2))),
+                            dict(type="delta", mixer=dict(heads=4, kv_heads=2, dim=16, vdim=32, conv=4),
+                                 mlp=dict(kind="moe", expert=dict(ff=64), router=dict(experts=4, identity=1, top=2))),
+                            dict(type="attention",
+                                 mixer=dict(heads=4, kv_heads=2, dim=32, vdim=32, scale=0.18, q_temp=dict(coef=0.3, every=16)),
+                                 mlp=None)]),
+        init=dict(seed=11, std=0.08, norm_std=0.1, block_size=16)),
 }
 
 

@@ -13,13 +13,14 @@
 
 #define SW_MAX_TAPS 16
 #define SW_TOKENS 16            // tokens of a request a CTA takes: at least as many as a window holds rows of the past
-#define SW_GROUPS 16            // channel groups a CTA takes
+#define SW_GROUPS 32            // channel groups a CTA takes
+#define SW_TPT 4                // consecutive tokens a thread takes (its channels' weights are fetched once for them)
 
-// out_plain[t, c] = x[t, c]; out_conv[t, c] = x[t, c] + sum_j w[c, j] x[t - (taps - 1) + j, c].  A thread takes one token
-// and CH neighbouring channels (one 16-byte load a row where CH = 4); the rows it shares with its neighbours come from
-// L1/L2.  Rows before the step's first come from the request's state (zeros for a request without context).  The CTA of a
-// request's first tokens is the only reader of the state and, behind a barrier, also its writer (a portion shorter than
-// the window shifts the old rows: they are read before the barrier and written after a second one).
+// out_plain[t, c] = x[t, c]; out_conv[t, c] = x[t, c] + sum_j w[c, j] x[t - (taps - 1) + j, c].  A thread takes SW_TPT
+// consecutive tokens and CH neighbouring channels (one 16-byte load a row where CH = 4); the rows it shares with its
+// neighbours come from L1/L2.  Rows before the step's first come from the request's state (zeros for a request without
+// context).  The CTA of a request's first tokens is the only reader of the state and, behind a barrier, also its writer (a
+// portion shorter than the window shifts the old rows: they are read before the barrier and written after it).
 template <int CH> struct SwVec { float v[CH]; };
 
 template <int CH>
@@ -44,36 +45,42 @@ __device__ __forceinline__ void sw_st(T* p, const SwVec<CH>& a) {
 }
 
 template <typename T, int CH>
-__global__ void __launch_bounds__(SW_TOKENS * SW_GROUPS)
+__global__ void __launch_bounds__(SW_TOKENS / SW_TPT * SW_GROUPS)
 stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ state,
                    const int* __restrict__ cu_q, const int* __restrict__ ctx_lens, const int* __restrict__ slot_ids,
                    T* __restrict__ out_plain, T* __restrict__ out_conv, int C, int taps, int write_state) {
+  constexpr int NCH = SW_GROUPS * CH;                 // channels of a CTA
+  __shared__ __align__(16) float ws[SW_MAX_TAPS * NCH];   // their weights, tap by tap: ws[j][channel]
   pdl_launch_dependents();
-  const int grp = threadIdx.x % SW_GROUPS, tok = threadIdx.x / SW_GROUPS;
-  const int c = (blockIdx.x * SW_GROUPS + grp) * CH;
+  const int grp = threadIdx.x % SW_GROUPS, quad = threadIdx.x / SW_GROUPS;
+  const int c0 = blockIdx.x * NCH;
+  const int c = c0 + grp * CH;
   const int req = blockIdx.y;
   const int hist = taps - 1;
   const bool in_c = c < C;
-  // the channels' weights depend on nothing a kernel writes
-  float wt[CH][SW_MAX_TAPS];
-#pragma unroll
-  for (int e = 0; e < CH; ++e)
-#pragma unroll
-    for (int j = 0; j < SW_MAX_TAPS; ++j) wt[e][j] = (in_c && j < taps) ? w[(size_t)(c + e) * taps + j] : 0.f;
+  // the channels' weights depend on nothing a kernel writes: one pass over the CTA's rows of w (they lie side by side)
+  {
+    const int n_w = min(NCH, C - c0) * taps;
+    const float* wsrc = w + (size_t)c0 * taps;
+    for (int i = threadIdx.x; i < n_w; i += blockDim.x) ws[(i % taps) * NCH + i / taps] = wsrc[i];
+  }
   pdl_wait();
+  __syncthreads();
   const int row0 = cu_q[req], n = cu_q[req + 1] - row0;
   if (blockIdx.z * SW_TOKENS >= n) return;            // (the whole CTA)
-  const int t = blockIdx.z * SW_TOKENS + tok;
   const int ctx = ctx_lens[req];
   float* st = (hist > 0 && in_c) ? state + (size_t)slot_ids[req] * hist * C + c : nullptr;      // [hist][C]: the oldest row first
-  if (in_c && t < n) {
-    SwVec<CH> acc;
+  const float* wmine = ws + grp * CH;
 #pragma unroll
-    for (int e = 0; e < CH; ++e) acc.v[e] = 0.f;
-    // taps in the order of time: the oldest row first, the token itself last
+  for (int i = 0; i < SW_TPT; ++i) {
+    const int t = blockIdx.z * SW_TOKENS + quad * SW_TPT + i;
+    if (in_c && t < n) {
+      SwVec<CH> acc;
 #pragma unroll
-    for (int j = 0; j < SW_MAX_TAPS - 1; ++j) {
-      if (j < hist) {
+      for (int e = 0; e < CH; ++e) acc.v[e] = 0.f;
+      // taps in the order of time: the oldest row first, the token itself last
+#pragma unroll 4
+      for (int j = 0; j < hist; ++j) {
         const int back = t - hist + j;
         SwVec<CH> r;
         if (back >= 0) r = sw_ld<CH>(x + (size_t)(row0 + back) * C + c);
@@ -82,35 +89,40 @@ stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, flo
 #pragma unroll
           for (int e = 0; e < CH; ++e) r.v[e] = 0.f;
         }
+        const SwVec<CH> wj = sw_ld<CH>(wmine + j * NCH);
 #pragma unroll
-        for (int e = 0; e < CH; ++e) acc.v[e] = fmaf(wt[e][j], r.v[e], acc.v[e]);
+        for (int e = 0; e < CH; ++e) acc.v[e] = fmaf(wj.v[e], r.v[e], acc.v[e]);
       }
-    }
-    const size_t at = (size_t)(row0 + t) * C + c;
-    const SwVec<CH> cur = sw_ld<CH>(x + at);
+      const size_t at = (size_t)(row0 + t) * C + c;
+      const SwVec<CH> cur = sw_ld<CH>(x + at);
+      const SwVec<CH> wl = sw_ld<CH>(wmine + hist * NCH);
 #pragma unroll
-    for (int e = 0; e < CH; ++e) {
-      float last = 0.f;
-#pragma unroll
-      for (int j = 0; j < SW_MAX_TAPS; ++j) if (j == hist) last = wt[e][j];
-      acc.v[e] = cur.v[e] + fmaf(last, cur.v[e], acc.v[e]);
+      for (int e = 0; e < CH; ++e) acc.v[e] = cur.v[e] + fmaf(wl.v[e], cur.v[e], acc.v[e]);
+      if (out_plain) sw_st<T, CH>(out_plain + at, cur);
+      sw_st<T, CH>(out_conv + at, acc);
     }
-    if (out_plain) sw_st<T, CH>(out_plain + at, cur);
-    sw_st<T, CH>(out_conv + at, acc);
   }
   if (blockIdx.z == 0 && write_state && hist > 0) {
-    // the last taps - 1 rows: from this step's rows and, where they are fewer, from the state as it was
-    const int j = tok;                                // thread (tok, grp) moves row j of the state
-    SwVec<CH> v;
+    // the last taps - 1 rows: from this step's rows and, where they are fewer, from the state as it was; thread (quad, grp)
+    // moves rows quad, quad + 4, ... of the state
+    SwVec<CH> v[SW_TPT];
 #pragma unroll
-    for (int e = 0; e < CH; ++e) v.v[e] = 0.f;
-    const int from = n - hist + j;                    // the step's row that lands in place j
-    if (in_c && j < hist) {
-      if (from >= 0) v = sw_ld<CH>(x + (size_t)(row0 + from) * C + c);
-      else if (ctx > 0) v = sw_ld<CH>(st + (size_t)(hist + from) * C);
+    for (int i = 0; i < SW_TPT; ++i) {
+      const int j = quad + i * (SW_TOKENS / SW_TPT);
+      const int from = n - hist + j;                  // the step's row that lands in place j
+#pragma unroll
+      for (int e = 0; e < CH; ++e) v[i].v[e] = 0.f;
+      if (in_c && j < hist) {
+        if (from >= 0) v[i] = sw_ld<CH>(x + (size_t)(row0 + from) * C + c);
+        else if (ctx > 0) v[i] = sw_ld<CH>(st + (size_t)(hist + from) * C);
+      }
     }
     __syncthreads();                                  // every read of the old rows is done
-    if (in_c && j < hist) sw_st<float, CH>(st + (size_t)j * C, v);
+#pragma unroll
+    for (int i = 0; i < SW_TPT; ++i) {
+      const int j = quad + i * (SW_TOKENS / SW_TPT);
+      if (in_c && j < hist) sw_st<float, CH>(st + (size_t)j * C, v[i]);
+    }
   }
 }
 
@@ -125,7 +137,7 @@ extern "C" int qe_stream_conv(const float* x, const float* w, float* state, cons
   const int per = vec ? 4 : 1;
   dim3 grid(((C + per - 1) / per + SW_GROUPS - 1) / SW_GROUPS, R, (max_q_len + SW_TOKENS - 1) / SW_TOKENS);
   if (grid.z > 65535) QE_REFUSE("stream_conv: a portion of %d tokens is too long", max_q_len);
-#define SCL(TT, CH) qe_launch(stream_conv_kernel<TT, CH>, grid, dim3(SW_TOKENS * SW_GROUPS), 0, stream, x, w, state, cu_q, ctx_lens, \
+#define SCL(TT, CH) qe_launch(stream_conv_kernel<TT, CH>, grid, dim3(SW_TOKENS / SW_TPT * SW_GROUPS), 0, stream, x, w, state, cu_q, ctx_lens, \
                               slot_ids, (TT*)out_plain, (TT*)out_conv, C, taps, write_state)
   if (dtype == QE_DTYPE_F32) { if (vec) SCL(float, 4); else SCL(float, 1); }
   else if (dtype == QE_DTYPE_BF16) { if (vec) SCL(__nv_bfloat16, 4); else SCL(__nv_bfloat16, 1); }
@@ -186,46 +198,65 @@ gated_norm_add_kernel(GnaArgs A) {
   }
 }
 
-// The same for bfloat16 branch, gate and copy on 8-byte boundaries with W a multiple of 4: four channels a thread and turn.
+// The same for bfloat16 branch, gate and copy on 8-byte boundaries with W a multiple of 4: four channels a thread and turn,
+// ITER turns a thread, everything a turn reads requested before anything is used (the row never leaves the registers).
+template <int ITER>
 __global__ void __launch_bounds__(256)
 gated_norm_add_bf16x4_kernel(GnaArgs A) {
-  extern __shared__ float sw_row[];
+  __shared__ float scratch[33];
   const int W4 = A.W >> 2;
-  float* scratch = sw_row + A.W;
   pdl_launch_dependents();
+  const float4* w4 = reinterpret_cast<const float4*>(A.w);
+  const float4* gb = reinterpret_cast<const float4*>(A.gate_bias);
+  float4 ww[ITER], bb[ITER];
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    ww[i] = d < W4 ? w4[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    bb[i] = (gb && A.gate && d < W4) ? gb[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   pdl_wait();
   const size_t base4 = (size_t)blockIdx.x * W4;
   const uint2* br = reinterpret_cast<const uint2*>(A.branch) + base4;
   const uint2* gt = A.gate ? reinterpret_cast<const uint2*>(A.gate) + base4 : nullptr;
-  const float4* gb = reinterpret_cast<const float4*>(A.gate_bias);
-  float4* row4 = reinterpret_cast<float4*>(sw_row);
+  const float4* src4 = reinterpret_cast<const float4*>(A.src) + base4;
   auto unpack = [](uint2 u) {
     const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
     const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
     return make_float4(a.x, a.y, b.x, b.y);
   };
+  uint2 rb[ITER], rg[ITER];
+  float4 s4[ITER];
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    rb[i] = make_uint2(0u, 0u); rg[i] = make_uint2(0u, 0u); s4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d < W4) { rb[i] = br[d]; if (gt) rg[i] = gt[d]; s4[i] = src4[d]; }
+  }
+  float4 v[ITER];
   float ss = 0.f;
-  for (int d = threadIdx.x; d < W4; d += blockDim.x) {
-    float4 v = unpack(br[d]);
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    v[i] = unpack(rb[i]);
     if (gt) {
-      float4 z = unpack(gt[d]);
-      if (gb) { const float4 bb = gb[d]; z.x += bb.x; z.y += bb.y; z.z += bb.z; z.w += bb.w; }
-      v.x *= 1.f / (1.f + expf(-z.x)); v.y *= 1.f / (1.f + expf(-z.y)); v.z *= 1.f / (1.f + expf(-z.z)); v.w *= 1.f / (1.f + expf(-z.w));
+      float4 z = unpack(rg[i]);
+      z.x += bb[i].x; z.y += bb[i].y; z.z += bb[i].z; z.w += bb[i].w;
+      v[i].x *= 1.f / (1.f + expf(-z.x)); v[i].y *= 1.f / (1.f + expf(-z.y)); v[i].z *= 1.f / (1.f + expf(-z.z)); v[i].w *= 1.f / (1.f + expf(-z.w));
     }
-    row4[d] = v;
-    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
   }
   ss = block_sum(ss, scratch);
   const float rstd = rsqrtf(ss / (float)A.W + A.eps);
-  const float4* src4 = reinterpret_cast<const float4*>(A.src) + base4;
-  const float4* w4 = reinterpret_cast<const float4*>(A.w);
   float4* dst4 = reinterpret_cast<float4*>(A.dst) + base4;
   uint2* cast = A.dst_cast ? reinterpret_cast<uint2*>(A.dst_cast) + base4 : nullptr;
   const long stride4 = A.entry_stride >> 2;
-  for (int d = threadIdx.x; d < W4; d += blockDim.x) {
-    const float4 s4 = src4[d], v = row4[d], ww = w4[d];
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d >= W4) continue;
     float4 o;
-    o.x = s4.x + v.x * rstd * ww.x; o.y = s4.y + v.y * rstd * ww.y; o.z = s4.z + v.z * rstd * ww.z; o.w = s4.w + v.w * rstd * ww.w;
+    o.x = s4[i].x + v[i].x * rstd * ww[i].x; o.y = s4[i].y + v[i].y * rstd * ww[i].y;
+    o.z = s4[i].z + v[i].z * rstd * ww[i].z; o.w = s4[i].w + v[i].w * rstd * ww[i].w;
     dst4[d] = o;
     if (cast) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
@@ -262,10 +293,17 @@ extern "C" int qe_gated_norm_add(const float* src, const void* branch, int branc
   const int threads = W >= 1024 ? 256 : W >= 256 ? 128 : 64;
   const uintptr_t all = (uintptr_t)src | (uintptr_t)dst | (uintptr_t)w | (uintptr_t)gate_bias | (uintptr_t)history | (uintptr_t)mixed;
   const uintptr_t half = (uintptr_t)branch | (uintptr_t)gate | (uintptr_t)dst_cast;
-  if (W % 4 == 0 && branch_dtype == QE_DTYPE_BF16 && (!gate || gate_dtype == QE_DTYPE_BF16) && (!dst_cast || cast_dtype == QE_DTYPE_BF16) &&
-      (all & 15) == 0 && (half & 7) == 0)
-    qe_launch(gated_norm_add_bf16x4_kernel, dim3(T), dim3(W >= 2048 ? 256 : W >= 512 ? 128 : 64), smem, stream, A);
-  else
+  if (W % 4 == 0 && W <= 8192 && branch_dtype == QE_DTYPE_BF16 && (!gate || gate_dtype == QE_DTYPE_BF16) &&
+      (!dst_cast || cast_dtype == QE_DTYPE_BF16) && (all & 15) == 0 && (half & 7) == 0) {
+    // two turns a thread where the row allows (more loads on their way a thread, fewer threads to meet at the sum)
+    const int W4 = W / 4;
+    const int vthreads = W4 <= 64 ? 32 : W4 <= 128 ? 64 : W4 <= 512 ? 128 : 256;
+    const int iters = (W4 + vthreads - 1) / vthreads;
+    if (iters <= 1) qe_launch(gated_norm_add_bf16x4_kernel<1>, dim3(T), dim3(vthreads), 0, stream, A);
+    else if (iters <= 2) qe_launch(gated_norm_add_bf16x4_kernel<2>, dim3(T), dim3(vthreads), 0, stream, A);
+    else if (iters <= 4) qe_launch(gated_norm_add_bf16x4_kernel<4>, dim3(T), dim3(vthreads), 0, stream, A);
+    else qe_launch(gated_norm_add_bf16x4_kernel<8>, dim3(T), dim3(vthreads), 0, stream, A);
+  } else
     qe_launch(gated_norm_add_kernel, dim3(T), dim3(threads), smem, stream, A);
   QE_CHECK_LAUNCH("gated_norm_add");
   return 0;

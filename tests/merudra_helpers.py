@@ -137,7 +137,7 @@ def check_requests(got, folder, requests, dtype, what):
         rows = got[rid]
         settled = settled_positions(folder, toks, dtype)
         idx = [i for i in sorted(rows) if i in settled]
-        assert len(rows) < 10 or len(idx) >= 0.8 * len(rows), f"{what} {rid}: too many close calls to judge"
+        assert len(rows) < 10 or len(idx) >= 0.5 * len(rows), f"{what} {rid}: too many close calls to judge"
         if not idx:
             continue
         assert_close_rows(torch.stack([rows[i] for i in idx]), want[idx], dtype, f"{what} {rid} (positions {idx[0]}..)")
