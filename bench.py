@@ -511,6 +511,92 @@ def merudra_config_of(sz: dict) -> dict:
                 token_side=dict(dim=64), layers=four * (sz["layers"] // 4))
 
 
+def merudra_kernels_alone(torch, ops, peaks) -> dict:
+    """The kernels that Merudra's arrangement adds, each alone on rows that do not fit in L2 (16 384 tokens of width
+    2 048: a float32 stream of 134 MB), beside the like kernel of the other models on the same rows: device time (CUDA
+    events, ten launches after three), the bytes the operation has to move, and their rate over the measured copy rate."""
+    from types import SimpleNamespace
+    dev, bf, f32 = "cuda:0", torch.bfloat16, torch.float32
+    T, W, taps, reqs = 16384, 2048, 4, 8
+    hbm = float(peaks["hbm_gbs"])
+    g = torch.Generator(device=dev).manual_seed(5)
+    rnd = lambda *shape, dtype=f32, std=1.0: (torch.randn(*shape, device=dev, dtype=f32, generator=g) * std).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    per = T // reqs
+    ctx = SimpleNamespace(cu_q=i32([r * per for r in range(reqs + 1)]), ctx_lens=i32([0] * reqs), slot_ids=i32(list(range(reqs))),
+                          num_reqs=reqs, max_q_len=per)
+    out: dict = {}
+
+    def timed(name, fn, nbytes, like=None):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 100.0
+        out[name] = {"us": round(us, 1), "mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / us / 1e3, 1),
+                     "frac_of_copy": round(nbytes / us / 1e3 / hbm, 3)}
+        if like:
+            out[name]["like"] = like
+
+    n = T * W
+    stream, stream2 = rnd(T, W), rnd(T, W)
+    branch, gate, cast, plain = rnd(T, W, dtype=bf), rnd(T, W, dtype=bf), torch.empty(T, W, device=dev, dtype=bf), torch.empty(T, W, device=dev, dtype=bf)
+    wt, gb = rnd(W) + 1.0, rnd(W)
+    cw = rnd(W, taps, std=0.3)
+    state = torch.zeros(reqs, taps - 1, W, device=dev, dtype=f32)
+    timed("add_rmsnorm", lambda: ops.add_rmsnorm(stream, branch, wt, 1e-6, cast), n * 12)
+    timed("gated_norm_add", lambda: ops.gated_norm_add(stream, branch, gate, gb, wt, 1e-6, stream2, cast), n * 14, like="add_rmsnorm")
+    timed("gated_norm_add without the rounded copy", lambda: ops.gated_norm_add(stream, branch, gate, gb, wt, 1e-6, stream2), n * 12,
+          like="add_rmsnorm")
+    timed("stream_conv", lambda: ops.stream_conv(stream, cw, state, ctx, plain, cast), n * 8, like="add_rmsnorm, short_conv")
+    xin, conv_out = rnd(T, W, dtype=bf), stream2
+    timed("short_conv", lambda: ops.short_conv(xin, cw, state, ctx, conv_out), n * 6)
+    count = 5
+    hist = rnd(count, T // 2, W)
+    dw, mixed = rnd(count), torch.empty(T // 2, W, device=dev, dtype=f32)
+    timed("depth_mix of five results", lambda: ops.depth_mix(hist, dw, count, mixed), (n // 2) * 4 * (count + 1), like="add_rmsnorm")
+    half = n // 2
+    timed("gated_norm_add with the weighted sum of five results",
+          lambda: ops.gated_norm_add(hist[count - 1], branch[:T // 2], None, None, wt, 1e-6, hist[count - 1], None,
+                                     depth_mix=(hist, dw, count, mixed)),
+          half * (4 + 2 + 4 + 4 * (count - 1) + 4), like="add_rmsnorm")
+    del hist, mixed
+    d, V = 64, 32768
+    Tt = T * 16
+    tg, table, tout = rnd(Tt, d, dtype=bf), rnd(V, d, dtype=bf), torch.empty(Tt, d, device=dev, dtype=bf)
+    ids = torch.randint(0, V, (Tt,), device=dev, dtype=torch.int32, generator=g)
+    timed("token_side_gate", lambda: ops.token_side_gate(tg, table, ids, tout), Tt * (d * 6 + 4), like="act_mul")
+    a_in, a_out = rnd(T, 2 * W, dtype=bf), torch.empty(T, W, device=dev, dtype=bf)
+    timed("act_mul", lambda: ops.act_mul(a_in, a_out), n * 6)
+    del tg, tout, a_in, a_out
+    Hq, Hkv, D, page = 16, 8, 128, 16
+    pos = torch.arange(T, device=dev, dtype=torch.int32) % per
+    slots = torch.arange(T, device=dev, dtype=torch.int32)
+    pages = torch.empty(T // page, 2, Hkv, page, D, device=dev, dtype=bf)
+    proj = rnd(T, (2 * Hq + Hkv) * D, dtype=bf)
+    qb, kb = rnd(Hq * D), rnd(Hkv * D)
+    moved = T * ((Hq + Hkv) * D * 2 * 2 + 2 * Hkv * D * 2)
+    timed("qk_bias_norm_kv_write", lambda: ops.qk_bias_norm_kv_write(proj, pos, qb, kb, 1e-6, (0.1, 512), pages, slots, Hq, Hkv, D),
+          moved, like="qk_norm_rope_kv_write")
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=bf)
+    nw = rnd(D) + 1.0
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=dev, dtype=f32) / D))
+    moved = T * ((Hq + Hkv) * D * 2 * 2 + Hkv * D * 2 + 2 * Hkv * D * 2)
+    timed("qk_norm_rope_kv_write", lambda: ops.qk_norm_rope_kv_write(qkv, pos, nw, nw, 1e-6, inv, D, pages, slots, Hq, Hkv, D), moved)
+    E, top = 10, 2
+    rx, rw, corr = rnd(T, W, dtype=bf), rnd(E, W, std=0.05), rnd(E, std=0.01)
+    ti, tw = torch.empty(T, top, device=dev, dtype=torch.int32), torch.empty(T, top, device=dev, dtype=f32)
+    timed("moe_route over all outputs", lambda: ops.moe_route(rx, rw, None, ti, tw, "softmax_all", corr), n * 2, like="moe_route over the chosen")
+    timed("moe_route over the chosen", lambda: ops.moe_route(rx, rw, None, ti, tw, "softmax_chosen"), n * 2)
+    ops.check_device_status()
+    return {"rows": T, "width": W, "kernels": out}
+
+
 def compare_designs(args) -> int:
     """``--compare ganidra``: prefill and decode of a Ganidra model beside a Qwen3 model of equal sizes (random weights,
     bfloat16), and the device time of every class of operation in one eager step of each (CUDA events around every
@@ -635,12 +721,13 @@ def compare_designs(args) -> int:
             g, q = out[name][designs[0]], out[name][other]
             out[name][f"{designs[0]}_over_{other}"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
                                                       "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
+    alone = merudra_kernels_alone(torch, ops, peaks) if args.compare == "merudra" and not args.compare_size else None
     clocks.stop()
     title = {"besavik": "Besavik beside Ganidra and Qwen3", "merudra": "Merudra beside Besavik and Qwen3"}.get(args.compare, "Ganidra beside Qwen3")
     print(json.dumps({"metric": f"prefill and decode tok/s, {title} at equal sizes", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2",
                       "steps": args.steps, "warmup": args.warmup, "peaks": peaks_src, "sizes": out,
-                      "clocks": clocks.summary([(m_start, clocks.mark())])}))
+                      **({"kernels_alone": alone} if alone else {}), "clocks": clocks.summary([(m_start, clocks.mark())])}))
     return 0
 
 

@@ -44,7 +44,23 @@ __device__ __forceinline__ void sw_st(T* p, const SwVec<CH>& a) {
   }
 }
 
-template <typename T, int CH>
+__device__ __forceinline__ void sw_unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 sw_pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+// TAPS 1 to 4: the window's length is known to the compiler, and a thread fetches each of the SW_TPT + TAPS - 1 rows that
+// its tokens read once, all of them requested before the first product.  TAPS 0: any length, row by row.  Both add the
+// products in the same order, so they agree to the bit.
+template <typename T, int CH, int TAPS>
 __global__ void __launch_bounds__(SW_TOKENS / SW_TPT * SW_GROUPS)
 stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ state,
                    const int* __restrict__ cu_q, const int* __restrict__ ctx_lens, const int* __restrict__ slot_ids,
@@ -71,6 +87,42 @@ stream_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, flo
   const int ctx = ctx_lens[req];
   float* st = (hist > 0 && in_c) ? state + (size_t)slot_ids[req] * hist * C + c : nullptr;      // [hist][C]: the oldest row first
   const float* wmine = ws + grp * CH;
+  if constexpr (TAPS > 0) {
+    constexpr int HIST = TAPS - 1;
+    const int t0 = blockIdx.z * SW_TOKENS + quad * SW_TPT;
+    if (in_c && t0 < n) {
+      SwVec<CH> r[SW_TPT + HIST];
+#pragma unroll
+      for (int i = 0; i < SW_TPT + HIST; ++i) {
+        const int t = t0 - HIST + i;                  // (a row of the state where negative: HIST + t is its place there)
+#pragma unroll
+        for (int e = 0; e < CH; ++e) r[i].v[e] = 0.f;
+        if (t >= 0) { if (t < n) r[i] = sw_ld<CH>(x + (size_t)(row0 + t) * C + c); }
+        else if (ctx > 0) r[i] = sw_ld<CH>(st + (size_t)(HIST + t) * C);
+      }
+      SwVec<CH> wj[TAPS];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) wj[j] = sw_ld<CH>(wmine + j * NCH);
+#pragma unroll
+      for (int i = 0; i < SW_TPT; ++i) {
+        if (t0 + i >= n) break;
+        SwVec<CH> acc;
+#pragma unroll
+        for (int e = 0; e < CH; ++e) acc.v[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < HIST; ++j) {
+#pragma unroll
+          for (int e = 0; e < CH; ++e) acc.v[e] = fmaf(wj[j].v[e], r[i + j].v[e], acc.v[e]);
+        }
+        const SwVec<CH>& cur = r[i + HIST];
+#pragma unroll
+        for (int e = 0; e < CH; ++e) acc.v[e] = cur.v[e] + fmaf(wj[HIST].v[e], cur.v[e], acc.v[e]);
+        const size_t at = (size_t)(row0 + t0 + i) * C + c;
+        if (out_plain) sw_st<T, CH>(out_plain + at, cur);
+        sw_st<T, CH>(out_conv + at, acc);
+      }
+    }
+  } else
 #pragma unroll
   for (int i = 0; i < SW_TPT; ++i) {
     const int t = blockIdx.z * SW_TOKENS + quad * SW_TPT + i;
@@ -137,12 +189,15 @@ extern "C" int qe_stream_conv(const float* x, const float* w, float* state, cons
   const int per = vec ? 4 : 1;
   dim3 grid(((C + per - 1) / per + SW_GROUPS - 1) / SW_GROUPS, R, (max_q_len + SW_TOKENS - 1) / SW_TOKENS);
   if (grid.z > 65535) QE_REFUSE("stream_conv: a portion of %d tokens is too long", max_q_len);
-#define SCL(TT, CH) qe_launch(stream_conv_kernel<TT, CH>, grid, dim3(SW_TOKENS / SW_TPT * SW_GROUPS), 0, stream, x, w, state, cu_q, ctx_lens, \
-                              slot_ids, (TT*)out_plain, (TT*)out_conv, C, taps, write_state)
+#define SCK(TT, CH, TP) qe_launch(stream_conv_kernel<TT, CH, TP>, grid, dim3(SW_TOKENS / SW_TPT * SW_GROUPS), 0, stream, x, w, state, \
+                                  cu_q, ctx_lens, slot_ids, (TT*)out_plain, (TT*)out_conv, C, taps, write_state)
+#define SCL(TT, CH) do { switch (taps) { case 1: SCK(TT, CH, 1); break; case 2: SCK(TT, CH, 2); break; case 3: SCK(TT, CH, 3); break; \
+                                         case 4: SCK(TT, CH, 4); break; default: SCK(TT, CH, 0); } } while (0)
   if (dtype == QE_DTYPE_F32) { if (vec) SCL(float, 4); else SCL(float, 1); }
   else if (dtype == QE_DTYPE_BF16) { if (vec) SCL(__nv_bfloat16, 4); else SCL(__nv_bfloat16, 1); }
   else QE_REFUSE("stream_conv: unknown dtype %d", dtype);
 #undef SCL
+#undef SCK
   QE_CHECK_LAUNCH("stream_conv");
   return 0;
 }
@@ -241,7 +296,9 @@ gated_norm_add_bf16x4_kernel(GnaArgs A) {
     if (gt) {
       float4 z = unpack(rg[i]);
       z.x += bb[i].x; z.y += bb[i].y; z.z += bb[i].z; z.w += bb[i].w;
-      v[i].x *= 1.f / (1.f + expf(-z.x)); v[i].y *= 1.f / (1.f + expf(-z.y)); v[i].z *= 1.f / (1.f + expf(-z.z)); v[i].w *= 1.f / (1.f + expf(-z.w));
+      // (the gate's logits are bfloat16 roundings: the hardware's exponential and quotient change nothing that counts)
+      v[i].x = __fdividef(v[i].x, 1.f + __expf(-z.x)); v[i].y = __fdividef(v[i].y, 1.f + __expf(-z.y));
+      v[i].z = __fdividef(v[i].z, 1.f + __expf(-z.z)); v[i].w = __fdividef(v[i].w, 1.f + __expf(-z.w));
     }
     ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
   }
@@ -328,10 +385,62 @@ __global__ void token_side_gate_kernel(const T* __restrict__ gate, const T* __re
   }
 }
 
+// bfloat16 rows whose d is a multiple of 8, on 16-byte boundaries: a 16-byte piece a thread and turn, two turns' loads on
+// their way together; gelu_tanh(g) = g sigmoid(2 u) with u = sqrt(2/pi) (g + 0.044715 g^3), by the hardware's exponential
+// and quotient (the result is rounded to bfloat16)
+__global__ void token_side_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ table,
+                                              const int* __restrict__ ids, __nv_bfloat16* __restrict__ out, unsigned total8,
+                                              unsigned d8, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned stride = gridDim.x * blockDim.x;
+  const uint4* g4 = reinterpret_cast<const uint4*>(gate);
+  const uint4* t4 = reinterpret_cast<const uint4*>(table);
+  uint4* o4 = reinterpret_cast<uint4*>(out);
+  const uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
+  for (unsigned e0 = blockIdx.x * blockDim.x + threadIdx.x; e0 < total8; e0 += 2 * stride) {
+    const unsigned e1 = e0 + stride;
+    const bool two = e1 < total8 && e1 > e0;
+    const unsigned r0 = e0 / d8, r1 = two ? e1 / d8 : r0;
+    const int id0 = __ldg(ids + r0), id1 = __ldg(ids + r1);
+    const uint4 rg0 = __ldcg(g4 + e0), rg1 = __ldcg(g4 + (two ? e1 : e0));
+    const uint4 rt0 = (id0 >= 0 && id0 < V) ? __ldg(t4 + (size_t)id0 * d8 + (e0 - r0 * d8)) : nan4;
+    const uint4 rt1 = (id1 >= 0 && id1 < V) ? __ldg(t4 + (size_t)id1 * d8 + ((two ? e1 : e0) - r1 * d8)) : nan4;
+    float g[8], e[8];
+    sw_unpack8(rg0, g);
+    sw_unpack8(rt0, e);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float u = 0.7978845608028654f * (g[k] + 0.044715f * g[k] * g[k] * g[k]);
+      g[k] = __fdividef(g[k], 1.f + __expf(-2.f * u)) * e[k];
+    }
+    o4[e0] = sw_pack8(g);
+    if (two) {
+      sw_unpack8(rg1, g);
+      sw_unpack8(rt1, e);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float u = 0.7978845608028654f * (g[k] + 0.044715f * g[k] * g[k] * g[k]);
+        g[k] = __fdividef(g[k], 1.f + __expf(-2.f * u)) * e[k];
+      }
+      o4[e1] = sw_pack8(g);
+    }
+  }
+}
+
 extern "C" int qe_token_side_gate(const void* gate, const void* table, const int* ids, void* out, int T, int d, int V, int dtype,
                                   cudaStream_t stream) {
   if (T <= 0 || d <= 0) return 0;
   const long total = (long)T * d;
+  if (dtype == QE_DTYPE_BF16 && d % 8 == 0 && total / 8 < (1L << 30) &&
+      (((uintptr_t)gate | (uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+    const unsigned total8 = (unsigned)(total / 8);
+    const unsigned vblocks = (total8 + 255) / 256 < 148 * 8 ? (total8 + 255) / 256 : 148 * 8;
+    qe_launch(token_side_gate_bf16x8_kernel, dim3(vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate,
+              (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, total8, (unsigned)(d / 8), V);
+    QE_CHECK_LAUNCH("token_side_gate");
+    return 0;
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
 #define TS(TT) qe_launch(token_side_gate_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gate, (const TT*)table, ids, (TT*)out, total, d, V)
   if (dtype == QE_DTYPE_F32) TS(float);

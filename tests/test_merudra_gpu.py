@@ -65,7 +65,7 @@ def _rows_of(cuts, r):
 
 # ---- what a sublayer reads: the stream and its short convolution ------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("C,taps", [(5, 1), (40, 2), (130, 3), (24, 5), (300, 16)])
+@pytest.mark.parametrize("C,taps", [(5, 1), (40, 2), (130, 3), (132, 4), (24, 5), (300, 16)])
 def test_stream_convolution_in_portions_through_used_slots(ops, dtype, C, taps):
     """Four unequal requests cut differently into three steps (portions shorter than the window among them), through
     slots that held other requests' rows: every row is the stream plus its convolution over the request's own rows."""
@@ -159,7 +159,7 @@ def test_the_last_add_of_a_layer_also_forms_the_weighted_sum(ops, dtype, L, T, W
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,d,V", [(1, 3, 7), (40, 24, 100), (300, 64, 50)])
+@pytest.mark.parametrize("T,d,V", [(1, 3, 7), (40, 24, 100), (300, 64, 50), (1, 8, 9), (2500, 16, 33), (40000, 64, 1000)])
 def test_token_side_gate(ops, dtype, T, d, V):
     g = torch.Generator().manual_seed(T + d)
     gate = (2.0 * torch.randn(T, d, generator=g)).to(dtype)
