@@ -255,7 +255,10 @@ gated_norm_add_kernel(GnaArgs A) {
 
 // The same for bfloat16 branch, gate and copy on 8-byte boundaries with W a multiple of 4: four channels a thread and turn,
 // ITER turns a thread, everything a turn reads requested before anything is used (the row never leaves the registers).
-template <int ITER>
+// PRE: the norm's weights and the gate's bias are fetched before the wait for the kernel ahead (steps of a few rows, where the
+// launch chain's gaps count); otherwise they are fetched where they are used, from L1, and the registers they would hold
+// while the row's loads are on their way go to more resident CTAs (steps of many rows, where bytes on their way count).
+template <int ITER, bool PRE>
 __global__ void __launch_bounds__(256)
 gated_norm_add_bf16x4_kernel(GnaArgs A) {
   __shared__ float scratch[33];
@@ -263,12 +266,14 @@ gated_norm_add_bf16x4_kernel(GnaArgs A) {
   pdl_launch_dependents();
   const float4* w4 = reinterpret_cast<const float4*>(A.w);
   const float4* gb = reinterpret_cast<const float4*>(A.gate_bias);
-  float4 ww[ITER], bb[ITER];
+  float4 ww[PRE ? ITER : 1], bb[PRE ? ITER : 1];
+  if constexpr (PRE) {
 #pragma unroll
-  for (int i = 0; i < ITER; ++i) {
-    const int d = threadIdx.x + i * blockDim.x;
-    ww[i] = d < W4 ? w4[d] : make_float4(0.f, 0.f, 0.f, 0.f);
-    bb[i] = (gb && A.gate && d < W4) ? gb[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < ITER; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      ww[i] = d < W4 ? w4[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+      bb[i] = (gb && A.gate && d < W4) ? gb[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   pdl_wait();
   const size_t base4 = (size_t)blockIdx.x * W4;
@@ -295,7 +300,9 @@ gated_norm_add_bf16x4_kernel(GnaArgs A) {
     v[i] = unpack(rb[i]);
     if (gt) {
       float4 z = unpack(rg[i]);
-      z.x += bb[i].x; z.y += bb[i].y; z.z += bb[i].z; z.w += bb[i].w;
+      const int d = threadIdx.x + i * blockDim.x;
+      const float4 b = PRE ? bb[i] : ((gb && d < W4) ? __ldg(gb + d) : make_float4(0.f, 0.f, 0.f, 0.f));
+      z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w;
       // (the gate's logits are bfloat16 roundings: the hardware's exponential and quotient change nothing that counts)
       v[i].x = __fdividef(v[i].x, 1.f + __expf(-z.x)); v[i].y = __fdividef(v[i].y, 1.f + __expf(-z.y));
       v[i].z = __fdividef(v[i].z, 1.f + __expf(-z.z)); v[i].w = __fdividef(v[i].w, 1.f + __expf(-z.w));
@@ -311,9 +318,10 @@ gated_norm_add_bf16x4_kernel(GnaArgs A) {
   for (int i = 0; i < ITER; ++i) {
     const int d = threadIdx.x + i * blockDim.x;
     if (d >= W4) continue;
+    const float4 wv = PRE ? ww[i] : __ldg(w4 + d);
     float4 o;
-    o.x = s4[i].x + v[i].x * rstd * ww[i].x; o.y = s4[i].y + v[i].y * rstd * ww[i].y;
-    o.z = s4[i].z + v[i].z * rstd * ww[i].z; o.w = s4[i].w + v[i].w * rstd * ww[i].w;
+    o.x = s4[i].x + v[i].x * rstd * wv.x; o.y = s4[i].y + v[i].y * rstd * wv.y;
+    o.z = s4[i].z + v[i].z * rstd * wv.z; o.w = s4[i].w + v[i].w * rstd * wv.w;
     dst4[d] = o;
     if (cast) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
@@ -356,10 +364,13 @@ extern "C" int qe_gated_norm_add(const float* src, const void* branch, int branc
     const int W4 = W / 4;
     const int vthreads = W4 <= 64 ? 32 : W4 <= 128 ? 64 : W4 <= 512 ? 128 : 256;
     const int iters = (W4 + vthreads - 1) / vthreads;
-    if (iters <= 1) qe_launch(gated_norm_add_bf16x4_kernel<1>, dim3(T), dim3(vthreads), 0, stream, A);
-    else if (iters <= 2) qe_launch(gated_norm_add_bf16x4_kernel<2>, dim3(T), dim3(vthreads), 0, stream, A);
-    else if (iters <= 4) qe_launch(gated_norm_add_bf16x4_kernel<4>, dim3(T), dim3(vthreads), 0, stream, A);
-    else qe_launch(gated_norm_add_bf16x4_kernel<8>, dim3(T), dim3(vthreads), 0, stream, A);
+#define GNA(IT) do { if (T <= 512) qe_launch(gated_norm_add_bf16x4_kernel<IT, true>, dim3(T), dim3(vthreads), 0, stream, A); \
+                     else qe_launch(gated_norm_add_bf16x4_kernel<IT, false>, dim3(T), dim3(vthreads), 0, stream, A); } while (0)
+    if (iters <= 1) GNA(1);
+    else if (iters <= 2) GNA(2);
+    else if (iters <= 4) GNA(4);
+    else GNA(8);
+#undef GNA
   } else
     qe_launch(gated_norm_add_kernel, dim3(T), dim3(threads), smem, stream, A);
   QE_CHECK_LAUNCH("gated_norm_add");

@@ -112,7 +112,8 @@ def test_stream_convolution_reads_a_state_it_does_not_write(ops):
 
 # ---- a sublayer's way back --------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,W,gated", [(1, 40, True), (9, 256, True), (70, 1024, True), (5, 3000, True), (33, 97, False)])
+@pytest.mark.parametrize("T,W,gated", [(1, 40, True), (9, 256, True), (70, 1024, True), (5, 3000, True), (33, 97, False),
+                                         (700, 512, True), (530, 2048, True), (600, 136, False), (513, 4100, True)])
 def test_gated_norm_add(ops, dtype, T, W, gated):
     g = torch.Generator().manual_seed(T + W)
     src = torch.randn(T, W, generator=g)
@@ -138,7 +139,7 @@ def test_gated_norm_add(ops, dtype, T, W, gated):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("L,T,W", [(1, 3, 40), (4, 9, 256), (7, 33, 97), (3, 70, 1024)])
+@pytest.mark.parametrize("L,T,W", [(1, 3, 40), (4, 9, 256), (7, 33, 97), (3, 70, 1024), (2, 520, 256)])
 def test_the_last_add_of_a_layer_also_forms_the_weighted_sum(ops, dtype, L, T, W):
     """The add into entry L of the layers' results, and the weighted sum over entries 0 .. L in the same launch: as the
     add alone followed by the sum alone, to the bit."""
