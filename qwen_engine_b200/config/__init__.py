@@ -3,9 +3,10 @@ from .qwen3_config import Qwen3Config
 from .ganidra_config import GanidraConfig
 from .besavik_config import BesavikConfig
 from .merudra_config import MerudraConfig
+from .pufivik_config import PufivikConfig
 from .engine_config import EngineConfig, parse_dtype
 from .presets import PRESETS, preset_config_dict, preset_init
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "GanidraConfig", "BesavikConfig", "MerudraConfig", "read_config_json",
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "GanidraConfig", "BesavikConfig", "MerudraConfig", "PufivikConfig", "read_config_json",
            "write_config_json", "EngineConfig", "parse_dtype", "PRESETS",
            "preset_config_dict", "preset_init"]

@@ -13,7 +13,8 @@ flash_attention_kernel(FaArgs args) {
 template <int D>
 __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const int* __restrict__ cu_q,
                                    const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                   int part_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv) {
+                                   int part_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
+                                   const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   const int* it = merge_items + 4 * blockIdx.x;
@@ -33,6 +34,7 @@ __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const in
       l += exp2f(part_ml[2 * slot] - m) * part_ml[2 * slot + 1];
     }
     const int ti = r / G, hg = r - ti * G;
+    if (sinks) l += exp2f(sinks[hkv * G + hg] * 1.4426950408889634f - m);      // the sink's share of the denominator
     __nv_bfloat16* dst = out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       float acc = 0.f;
@@ -50,7 +52,8 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
                         const int* cu_q, const int* ctx_lens, const int* items, int n_items,
                         const int* merge_items, int n_merge, void* out, float* part_acc, float* part_ml,
                         int part_rows, int* counters, float scale, int window, int Hq, int Hkv, int page_size,
-                        const float* slopes, int kv_planes, cudaStream_t stream) {
+                        const float* slopes, int kv_planes, float softcap, const float* sinks, int v_shift,
+                        cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(QROWS + 2 * STAGES * FA_BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
@@ -62,13 +65,14 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_items, Hkv);
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
-            (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale_log2, window, Hq, Hkv, page_size, slopes, kv_planes};
+            (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale_log2, window, Hq, Hkv, page_size, slopes, kv_planes,
+            softcap, scale, sinks, v_shift};
   qe_launch(flash_attention_kernel<D, STAGES, QROWS>, grid, dim3(2 * FA_THREADS), smem, stream, fa);
   QE_CHECK_LAUNCH("flash_attention");
   if (n_merge > 0 && counters == nullptr) {
     dim3 mgrid(n_merge, Hkv), mblock(32, 4);
     qe_launch(flash_merge_kernel<D>, mgrid, mblock, 0, stream, merge_items, cu_q, (const float*)part_acc,
-              (const float*)part_ml, part_rows, (__nv_bfloat16*)out, Hq, Hkv);
+              (const float*)part_ml, part_rows, (__nv_bfloat16*)out, Hq, Hkv, sinks);
     QE_CHECK_LAUNCH("flash_merge");
   }
   return 0;
@@ -97,7 +101,8 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               int n_items, const int* merge_items, int n_merge, void* out,
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
                                               int small_tiles, float scale, int window, int Hq, int Hkv, int D,
-                                              int page_size, const float* slopes, int kv_planes, cudaStream_t stream);
+                                              int page_size, const float* slopes, int kv_planes, float softcap,
+                                              const float* sinks, int v_shift, cudaStream_t stream);
 
 extern "C" int qe_flash_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
                                   int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
@@ -106,7 +111,7 @@ extern "C" int qe_flash_attention(const void* q, long q_stride, const void* page
                                   int page_size, cudaStream_t stream) {
   return qe_flash_attention_fused_merge(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items,
                                         merge_items, n_merge, out, part_acc, part_ml, part_rows, nullptr, 0, scale,
-                                        window, Hq, Hkv, D, page_size, nullptr, 2, stream);
+                                        window, Hq, Hkv, D, page_size, nullptr, 2, 0.f, nullptr, 0, stream);
 }
 
 extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, const void* pages, const int* block_tables,
@@ -114,15 +119,18 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               int n_items, const int* merge_items, int n_merge, void* out,
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
                                               int small_tiles, float scale, int window, int Hq, int Hkv, int D,
-                                              int page_size, const float* slopes, int kv_planes, cudaStream_t stream) {
+                                              int page_size, const float* slopes, int kv_planes, float softcap,
+                                              const float* sinks, int v_shift, cudaStream_t stream) {
   // small_tiles: every item has at most 16 rows (a decode step): 16 query rows are staged and the key
   // tiles run through a deeper pipeline
   if (n_items <= 0) return 0;
   if (!qe_flash_attention_supported(Hq, Hkv, D))
     QE_REFUSE("flash_attention: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
   if (((uintptr_t)q | (uintptr_t)pages) & 15 || (q_stride % 8)) QE_REFUSE("flash_attention: operands must be 16-byte aligned");
+  if (v_shift < 0 || v_shift >= Hkv || (v_shift && kv_planes == 1)) QE_REFUSE("flash_attention: a shift of %d over %d kv heads", v_shift, Hkv);
+  if (slopes && softcap > 0.f) QE_REFUSE("flash_attention: scores are biased by distance or bent, not both");
 #define FA_ARGS q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items, merge_items, n_merge, out, \
-      part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, slopes, kv_planes, stream
+      part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, slopes, kv_planes, softcap, sinks, v_shift, stream
 #define FA_CASE(DD) case DD: return small_tiles ? launch_flash<DD, 3, 16>(FA_ARGS) : launch_flash<DD, 2, FA_BM>(FA_ARGS);
   switch (D) {
     FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)

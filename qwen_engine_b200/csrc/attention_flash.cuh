@@ -70,7 +70,7 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
                                         int row_base, int kb0, int kt, int kv_begin, int kv_end, int pos_lo, int pos_hi,
                                         int window, float scale_log2, int lane, float& m_lo, float& m_hi, float& l_lo,
                                         float& l_hi, float (&o)[D / 8][4], bool all_allowed,
-                                        float slope_lo = 0.f, float slope_hi = 0.f) {
+                                        float slope_lo = 0.f, float slope_hi = 0.f, float cap_in = 0.f, float cap_out = 0.f) {
   constexpr int LD = D + 8, KS = D / 16;
   const int c = lane & 3;
   // ---- S = Q K^T ---------------------------------------------------------------------------
@@ -92,6 +92,17 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
     }
   }
   // ---- mask, online softmax --------------------------------------------------------------------
+  if (cap_in > 0.f) {
+    // scores bent towards +-cap: cap tanh(scale q.k / cap), in units of log2 e like every score here
+    // (cap_in = scale / cap, cap_out = cap log2 e); tanh z = 1 - 2 / (1 + e^(2 z)) with the hardware's exponential
+#pragma unroll
+    for (int i = 0; i < 2 * NB; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        s[i][e] = cap_out * (1.f - __fdividef(2.f, 1.f + exp2f(s[i][e] * cap_in * 2.8853900817779268f)));
+    }
+    scale_log2 = 1.f;
+  }
   float mx_lo = -INFINITY, mx_hi = -INFINITY;
   if (all_allowed) {
 #pragma unroll
@@ -176,7 +187,8 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
 template <int D>
 __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const float* part_ml, int part_rows, int first,
                                                int n, int hkv, int Hkv, int nrows, int G, int Hq,
-                                               __nv_bfloat16* out_row0 /* row of the tile's first token */) {
+                                               __nv_bfloat16* out_row0 /* row of the tile's first token */,
+                                               const float* sinks = nullptr) {
   for (int e = threadIdx.x; e < nrows * D; e += FA_THREADS) {       // the computing threads only
     const int r = e / D, d = e - r * D;
     float m = -INFINITY;
@@ -190,6 +202,7 @@ __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const floa
       acc += wgt * __ldcg(part_acc + slot * D + d);
     }
     const int ti = r / G, hg = r - ti * G;
+    if (sinks) l += exp2f(sinks[hkv * G + hg] * 1.4426950408889634f - m);      // the sink's share of the denominator
     out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }
 }
@@ -261,6 +274,10 @@ struct FaArgs {
   int* counters; float scale_log2; int window, Hq, Hkv, page_size;
   const float* slopes;      // null, or float32 [Hq]: slopes[h] * (position - key) is taken off the score (last: may be left out)
   int kv_planes;            // 1: a page holds one plane per kv head and the values are its channels (a latent cache); else keys and values apart
+  float softcap;            // above 0: the scaled score s becomes softcap * tanh(s / softcap)
+  float scale;              // the scale itself (scale_log2 / log2 e), for the bent scores
+  const float* sinks;       // null, or float32 [Hq]: exp(sinks[h]) joins head h's denominator (no key, no value)
+  int v_shift;              // the weights of a head of kv head c meet the values of kv head (c + v_shift) mod Hkv
 };
 
 // The work of one CTA (work item `item_idx`, kv head `hkv`) by 256 threads; `smem_raw`: the dynamic
@@ -338,6 +355,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
     const size_t page_stride = (size_t)(A.kv_planes == 1 ? 1 : 2) * Hkv * page_size * D;
     const size_t v_off = A.kv_planes == 1 ? 0 : (size_t)Hkv * page_size * D;
     const __nv_bfloat16* head_base = pages + (size_t)hkv * page_size * D;
+    const long v_head_off = ((long)((hkv + A.v_shift) % Hkv) - hkv) * page_size * D;     // values of another kv head (0: its own)
     bool waited = false;
     auto wait_and_fetch_q = [&]() {
       if (!PERSIST) pdl_wait();
@@ -377,7 +395,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
           else { blk = kj / page_size; off = kj - blk * page_size; }
           const __nv_bfloat16* src = head_base + (size_t)table[blk] * page_stride + off * D + ch * 8;
           cp_async16(dk + so, src);
-          if (!one_plane) cp_async16(dv + so, src + v_off);       // (one plane: the values are read where the keys landed)
+          if (!one_plane) cp_async16(dv + so, src + v_off + v_head_off);       // (one plane: the values are read where the keys landed)
         } else {
           *reinterpret_cast<uint4*>(dk + so) = make_uint4(0, 0, 0, 0);
           if (!one_plane) *reinterpret_cast<uint4*>(dv + so) = make_uint4(0, 0, 0, 0);
@@ -401,6 +419,8 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
   const bool biased = A.slopes != nullptr;
   const float slope_lo = biased && r_lo < nrows ? A.slopes[hkv * G + r_lo % G] * 1.4426950408889634f : 0.f;
   const float slope_hi = biased && r_hi < nrows ? A.slopes[hkv * G + r_hi % G] * 1.4426950408889634f : 0.f;
+  const float cap_in = A.softcap > 0.f ? A.scale / A.softcap : 0.f, cap_out = A.softcap * 1.4426950408889634f;
+  const float* __restrict__ sinks = A.sinks;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[D / 8][4];
 #pragma unroll
@@ -431,10 +451,10 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
                                        lane, m_lo, m_hi, l_lo, l_hi, o, all_allowed, slope_lo, slope_hi);
       } else if (keysplit)
         fa_tile<D, 1>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
-                      m_lo, m_hi, l_lo, l_hi, o, false);
+                      m_lo, m_hi, l_lo, l_hi, o, false, 0.f, 0.f, cap_in, cap_out);
       else
         fa_tile<D, FA_BN / 16>(sq, tk, tv, row_base, 0, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2,
-                               lane, m_lo, m_hi, l_lo, l_hi, o, all_allowed);
+                               lane, m_lo, m_hi, l_lo, l_hi, o, all_allowed, 0.f, 0.f, cap_in, cap_out);
     }
     __syncwarp();
     if (lane == 0) fa_bar_arrive(&bar_empty[stage]);      // this warp is done with the slot
@@ -471,6 +491,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
       }
       if (part < 0) {
         const int ti = r / G, hg = r - ti * G;
+        if (sinks) l += exp2f(sinks[hkv * G + hg] * 1.4426950408889634f - base);
         out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
       } else {
         const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
@@ -487,7 +508,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
       const int ti = r / G, hg = r - ti * G;
       const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
       if (part < 0) {
-        const float inv = 1.f / l;
+        const float inv = 1.f / (sinks ? l + exp2f(sinks[hkv * G + hg] * 1.4426950408889634f - m) : l);
         __nv_bfloat16* dst = out_row0 + (size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
@@ -518,7 +539,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
     fa_consumer_sync();
     if (s_last) {
       __threadfence();
-      fa_merge_parts<D>(part_acc, part_ml, part_rows, first, n_splits, hkv, Hkv, nrows, G, Hq, out_row0);
+      fa_merge_parts<D>(part_acc, part_ml, part_rows, first, n_splits, hkv, Hkv, nrows, G, Hq, out_row0, sinks);
     }
   }
   }   // ok

@@ -26,7 +26,8 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
                          const int* __restrict__ block_tables, int max_blocks,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                          const int* __restrict__ tiles, T* __restrict__ out, float scale, int window,
-                         int Hq, int Hkv, int D, int page_size, const float* __restrict__ slopes, int kv_planes) {
+                         int Hq, int Hkv, int D, int page_size, const float* __restrict__ slopes, int kv_planes,
+                         float softcap, const float* __restrict__ sinks, int v_shift) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -36,6 +37,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
   float* vs = ks + AG_BN * Dp;                // [AG_BN][D]
   const int tile = blockIdx.x, hq = blockIdx.y;
   const int hkv = hq / (Hq / Hkv);
+  const int hv = (hkv + v_shift) % Hkv;                 // the kv head whose values the head's weights meet (its own unless shifted)
   const float slope = slopes ? slopes[hq] : 0.f;        // distance bias: slope * (i - j) is taken off the score
   const int req = tiles[2 * tile], q0 = tiles[2 * tile + 1];
   const int row0 = cu_q[req];
@@ -75,7 +77,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
         // (kv_planes 1: a page holds one plane per kv head, and the values are its channels)
         const size_t base = ((((size_t)page * kv_planes) * Hkv + hkv) * page_size + (kj % page_size)) * D + d;
         kvl = to_f32(pages[base]);
-        vvl = kv_planes == 1 ? kvl : to_f32(pages[base + (size_t)Hkv * page_size * D]);
+        vvl = kv_planes == 1 ? kvl : to_f32(pages[base + ((size_t)Hkv + hv - hkv) * page_size * D]);
       }
       ks[j * Dp + d] = kvl;
       vs[j * D + d] = vvl;
@@ -92,7 +94,9 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
       const float* qr = qs + r * D;
       const float* kr = ks + lane * Dp;
       for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
-      s = ok ? fmaf(-slope, (float)(pos - kj), s * scale) : -INFINITY;
+      s *= scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);          // the score bent towards +-softcap
+      s = ok ? fmaf(-slope, (float)(pos - kj), s) : -INFINITY;
       const float tile_max = warp_max(s);
       if (tile_max == -INFINITY) continue;              // nothing allowed in this tile
       const float m_new = fmaxf(m[i], tile_max);
@@ -116,7 +120,8 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
   for (int i = 0; i < QPW; ++i) {
     const int r = warp * QPW + i;
     if (r >= nq) continue;
-    const float inv = 1.f / l[i];
+    // a sink: exp(sinks[head]) joins the denominator; it has no key and no value
+    const float inv = 1.f / (sinks ? l[i] + expf(sinks[hq] - m[i]) : l[i]);
     T* o = out + (size_t)(row0 + q0 + r) * ((size_t)Hq * D) + (size_t)hq * D;
 #pragma unroll
     for (int c = 0; c < DREG; ++c) {
@@ -130,7 +135,8 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
                                           const int* block_tables, int max_blocks, const int* cu_q,
                                           const int* ctx_lens, const int* tiles, int n_tiles, void* out,
                                           float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                          int dtype, const float* slopes, int kv_planes, cudaStream_t stream) {
+                                          int dtype, const float* slopes, int kv_planes, float softcap, const float* sinks,
+                                          int v_shift, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (D > AG_MAX_D || D < 1) QE_REFUSE("paged_attention: head_dim %d is outside 1..%d", D, AG_MAX_D);
   if (Hkv < 1 || Hq % Hkv) QE_REFUSE("paged_attention: %d query heads do not group over %d kv heads", Hq, Hkv);
@@ -149,9 +155,10 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
     configured = true;
   }
   const int planes = kv_planes == 1 ? 1 : 2;
+  if (v_shift < 0 || v_shift >= Hkv || (v_shift && planes == 1)) QE_REFUSE("paged_attention: a shift of %d over %d kv heads", v_shift, Hkv);
 #define AGL(TT, DR) qe_launch(attention_generic_kernel<TT, DR>, grid, dim3(AG_WARPS * 32), smem, stream, (const TT*)q, q_stride, \
                               (const TT*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles, (TT*)out, scale, window, Hq, Hkv, D, \
-                              page_size, slopes, planes)
+                              page_size, slopes, planes, softcap, sinks, v_shift)
   if (dtype == QE_DTYPE_F32) { if (D <= 512) AGL(float, 16); else AGL(float, AG_MAX_D / 32); }
   else if (dtype == QE_DTYPE_BF16) { if (D <= 512) AGL(__nv_bfloat16, 16); else AGL(__nv_bfloat16, AG_MAX_D / 32); }
   else QE_REFUSE("paged_attention: unknown dtype %d", dtype);

@@ -113,6 +113,11 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const flo
     if (lane == 0) { top_idx[(size_t)t * top + j] = at; z[at] = -INFINITY; }
     __syncwarp();
   }
+  if (scoring == 2) {
+    // every expert scored alone: sigmoid(z); the largest logits are the largest scores; the weights are the scores as they are
+    if (lane == 0) for (int j = 0; j < top; ++j) top_w[(size_t)t * top + j] = 1.f / (1.f + expf(-chosen[j]));
+    return;
+  }
   float sum = 0.f;
   for (int j = 0; j < top; ++j) { chosen[j] = expf(chosen[j] - zmax); sum += chosen[j]; }
   if (lane == 0) for (int j = 0; j < top; ++j) top_w[(size_t)t * top + j] = chosen[j] / sum;
@@ -122,7 +127,7 @@ extern "C" int qe_moe_route(const void* x, const float* w, const float* bias, in
                             int E, int top, int dtype, int scoring, const float* correction, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 1 || E > MOE_MAX_E || top < 1 || top > MOE_MAX_TOP || top > E) QE_REFUSE("moe_route: %d of %d experts", top, E);
-  if (scoring != 0 && scoring != 1) QE_REFUSE("moe_route: unknown scoring %d", scoring);
+  if (scoring < 0 || scoring > 2) QE_REFUSE("moe_route: unknown scoring %d", scoring);
   const size_t smem = ((size_t)((W + 3) & ~3) + 2 * (size_t)E) * sizeof(float);
   if (smem > 160 * 1024) QE_REFUSE("moe_route: a row of %d channels does not fit shared memory", W);
   static bool configured = false;
@@ -207,7 +212,8 @@ __device__ __forceinline__ float moe_glu(float v0, float v1, int act) {
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(TP_THREADS)
 moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* __restrict__ offsets,
-                   const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act) {
+                   const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act,
+                   const float* __restrict__ pair_w) {
   __shared__ TpSmem<T, GLU ? 2 : 1> sm;
   __shared__ int s_tile[4];
   TpAcc<T, GLU ? 2 : 1> acc;
@@ -233,7 +239,9 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* 
     if (r >= rows || n0 + n >= N) return;
     const size_t at = (size_t)(first + r) * N + n0 + n;
     if constexpr (GLU) {
-      const float y = moe_glu<T>(v0, v1, act);
+      // an expert that reads its weight times the token's row: the products are linear, so the weight meets their sums
+      const float pw = pair_w ? pair_w[sorted_pair[first + r]] : 1.f;
+      const float y = moe_glu<T>(v0 * pw, v1 * pw, act);
       ((T*)out_)[at] = from_f32<T>(y);
     } else {
       ((float*)out_)[at] = v0;
@@ -248,7 +256,7 @@ template <bool GLU>
 __global__ void __launch_bounds__(FP_THREADS)
 moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
                         const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act,
-                        int k_share, long share_stride) {
+                        int k_share, long share_stride, const float* __restrict__ pair_w) {
   extern __shared__ __align__(16) unsigned char fp_smem[];
   __shared__ int s_tile[4];
   FpAcc acc;
@@ -277,7 +285,10 @@ moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   fast_tile_for_each<NB>(acc, [&](int r, int n, float v0, float v1) {
     if (r >= rows || n0 + n >= N) return;
     const size_t at = (size_t)(first + r) * N + n0 + n;
-    if constexpr (GLU) ((__nv_bfloat16*)out_)[at] = __float2bfloat16_rn(moe_glu<__nv_bfloat16>(v0, v1, act));
+    if constexpr (GLU) {
+      const float pw = pair_w ? pair_w[sorted_pair[first + r]] : 1.f;
+      ((__nv_bfloat16*)out_)[at] = __float2bfloat16_rn(moe_glu<__nv_bfloat16>(v0 * pw, v1 * pw, act));
+    }
     else ((float*)out_)[(size_t)blockIdx.z * share_stride + at] = v0;
   });
 }
@@ -286,7 +297,7 @@ static int moe_tiles(int P, int E, int BM = TP_BM) { return (P + BM - 1) / BM + 
 
 template <bool GLU>
 static int moe_fast_launch(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* out, int P, int E, int N,
-                           int K, int top, int act, int shares, cudaStream_t stream) {
+                           int K, int top, int act, int shares, cudaStream_t stream, const float* pair_w = nullptr) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(moe_product_fast_kernel<GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM_BYTES);
@@ -297,7 +308,7 @@ static int moe_fast_launch(const void* x, const void* w, const int* offsets, con
   dim3 grid(moe_tiles(P, E, FP_BM), (N + BN - 1) / BN, shares);
   const int k_share = shares > 1 ? ((K + shares - 1) / shares + FP_BK - 1) / FP_BK * FP_BK : K;
   qe_launch(moe_product_fast_kernel<GLU>, grid, dim3(FP_THREADS), FP_SMEM_BYTES, stream, (const __nv_bfloat16*)x,
-            (const __nv_bfloat16*)w, offsets, sorted_pair, out, E, N, K, top, act, k_share, (long)P * N);
+            (const __nv_bfloat16*)w, offsets, sorted_pair, out, E, N, K, top, act, k_share, (long)P * N, pair_w);
   return 0;
 }
 static bool moe_fast_applies(const void* x, const void* w, int K, int dtype) {
@@ -305,16 +316,16 @@ static bool moe_fast_applies(const void* x, const void* w, int K, int dtype) {
 }
 
 extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* act_out,
-                              int P, int E, int I, int K, int top, int act, int dtype, cudaStream_t stream) {
+                              int P, int E, int I, int K, int top, int act, int dtype, const float* pair_w, cudaStream_t stream) {
   if (P <= 0) return 0;
   if (moe_fast_applies(x, w, K, dtype)) {
-    if (int rc = moe_fast_launch<true>(x, w, offsets, sorted_pair, act_out, P, E, I, K, top, act, 1, stream)) return rc;
+    if (int rc = moe_fast_launch<true>(x, w, offsets, sorted_pair, act_out, P, E, I, K, top, act, 1, stream, pair_w)) return rc;
     QE_CHECK_LAUNCH("moe_gate_up");
     return 0;
   }
   dim3 grid(moe_tiles(P, E), (I + TP_BN - 1) / TP_BN);
 #define MP(TT) qe_launch(moe_product_kernel<TT, true>, grid, dim3(TP_THREADS), 0, stream, (const TT*)x, (const TT*)w, offsets, \
-                         sorted_pair, act_out, E, I, K, top, act)
+                         sorted_pair, act_out, E, I, K, top, act, pair_w)
   if (dtype == QE_DTYPE_F32) MP(float);
   else if (dtype == QE_DTYPE_BF16) MP(__nv_bfloat16);
   else QE_REFUSE("moe_gate_up: unknown dtype %d", dtype);
@@ -345,7 +356,7 @@ extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets
   if (shares > 1) cudaMemsetAsync(y + (size_t)P * N, 0, (size_t)(shares - 1) * P * N * sizeof(float), stream);
   dim3 grid(moe_tiles(P, E), (N + TP_BN - 1) / TP_BN);
 #define MP(TT) qe_launch(moe_product_kernel<TT, false>, grid, dim3(TP_THREADS), 0, stream, (const TT*)act_in, (const TT*)w, offsets, \
-                         (const int*)nullptr, (void*)y, E, N, K, 1, 0)
+                         (const int*)nullptr, (void*)y, E, N, K, 1, 0, (const float*)nullptr)
   if (dtype == QE_DTYPE_F32) MP(float);
   else if (dtype == QE_DTYPE_BF16) MP(__nv_bfloat16);
   else QE_REFUSE("moe_down: unknown dtype %d", dtype);
@@ -374,7 +385,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
         v = src[0];
         for (int z = 1; z < shares; ++z) v += src[(size_t)z * share_stride];
       }
-      acc = fmaf(top_w[t * top + j], v, acc);
+      acc = top_w ? fmaf(top_w[t * top + j], v, acc) : acc + v;
     }
     out[e] = from_f32<T>(acc);
   }

@@ -227,10 +227,12 @@ class DecoderModel:
             # and the weights that the step reads first after this block
             nxt = lo.plan[i + 1].layer if i + 1 < len(lo.plan) else None
             ctx.extras["weights_after_ffn"] = self.blocks[nxt].first_weights() if nxt is not None else None
+            # and the norm that reads the stream first after this block, where the next block names it
+            ctx.extras["norm_after_block"] = self.blocks[nxt].first_norm() if nxt is not None else None
             if history is not None:
                 history.run = i
             self.blocks[entry.layer].forward(ctx, stream, view, group, entry.write_cache)
-        ctx.extras["next_cache"] = ctx.extras["weights_after_ffn"] = None
+        ctx.extras["next_cache"] = ctx.extras["weights_after_ffn"] = ctx.extras["norm_after_block"] = None
         if ctx.num_logit_rows == 0:
             return None
         N = ctx.num_logit_rows

@@ -803,12 +803,15 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
                           k_norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor],
                           rotary_dim: int, kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
                           num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True,
-                          cos_sin: Optional[torch.Tensor] = None, norm_dim: Optional[int] = None) -> None:
+                          cos_sin: Optional[torch.Tensor] = None, norm_dim: Optional[int] = None, magnitude: float = 1.0,
+                          value_mix=None) -> None:
     """On the stacked projection output qkv [T, (Hq + 2 Hkv) D] (rows may be strided: the leading columns
     of a wider product), in place: per-head RMS norm of q and k (if weights are given), half-split rotation
     by positions (if inv_freq is given); then k and v are written to the slots of ``slot_mapping`` in
     ``kv_pages`` [pages, 2, Hkv, page, D].  ``norm_dim``: the channels the norm's mean runs over, where a
-    head is padded with zero channels up to D."""
+    head is padded with zero channels up to D.  ``magnitude``: cosines and sines are multiplied by it.
+    ``value_mix``: values shared across layers, ("keep", first) copies this layer's values of the step's tokens into
+    ``first`` [T, Hkv D]; ("blend", first, lam) caches (1 - lam) v + lam first in the place of v."""
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     _need(qkv.shape == (T, (Hq + 2 * Hkv) * D) and qkv.stride(1) == 1, "qk_norm_rope_kv_write: qkv must be [T, (Hq+2Hkv)D]")
@@ -831,13 +834,21 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
               "qk_norm_rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
+    v_first, v_mode, v_lambda = None, 0, 0.0
+    if value_mix is not None:
+        _need(value_mix[0] in ("keep", "blend"), "qk_norm_rope_kv_write: value_mix is ('keep', first) or ('blend', first, lam)")
+        v_first, v_mode = value_mix[1], 1 if value_mix[0] == "keep" else 2
+        v_lambda = float(value_mix[2]) if v_mode == 2 else 0.0
+        _need(v_first.shape == (T, Hkv * D) and v_first.dtype == qkv.dtype and v_first.is_contiguous(),
+              "qk_norm_rope_kv_write: the shared values must be contiguous [T, Hkv D] in qkv's dtype")
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
         _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(inv_freq),
         _ptr(cos_sin if (cos_sin is not None and D == 128 and rotary_dim == D) else None), int(rotary_dim),
         _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
-        T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), int(norm_dim or D), _stream()), "qk_norm_rope_kv_write")
+        T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), int(norm_dim or D), ctypes.c_float(magnitude), _ptr(v_first),
+        v_mode, ctypes.c_float(v_lambda), _stream()), "qk_norm_rope_kv_write")
 
 
 def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
@@ -852,7 +863,8 @@ def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fre
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(0),
         ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(0), _ptr(positions),
         _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), _ptr(None), int(rotary_dim),
-        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), D, _stream()), "rope_neox")
+        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), D, ctypes.c_float(1.0), _ptr(None), 0, ctypes.c_float(0.0),
+        _stream()), "rope_neox")
 
 
 def flash_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -923,6 +935,13 @@ def geometry_planes(geo) -> int:
     return int(geo[5]) if len(geo) > 5 else 2
 
 
+def geometry_plain_kernels(geo) -> bool:
+    """The seventh entry of a geometry, if it has one: the mixer bends its scores, keeps a sink in the denominator or lets
+    a head's weights meet another kv head's values, which the flash and the generic kernel do and the kernels for head
+    size 128 alone do not."""
+    return bool(len(geo) > 6 and geo[6])
+
+
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                    geometries=(), dtype: torch.dtype = torch.float32,
                    uniform_splits: Optional[dict] = None) -> dict[str, list[int]]:
@@ -949,7 +968,8 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        use_tc = uniform_splits is None and geometry_planes(geo) == 2 and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
+        use_tc = (uniform_splits is None and geometry_planes(geo) == 2 and not geometry_plain_kernels(geo)
+                  and tc_attention_supported(dtype, Hq, Hkv, D, page_size))
         on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
         tc_tiles: list = []
         base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
@@ -1013,7 +1033,7 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
         span = min(max_tokens, window) if window else max_tokens
         target = FLASH_TARGET_CTAS
         if (DECODE_ATTENTION_MMA and DECODE_ATTENTION_MMA_WIDE and dtype == torch.bfloat16 and D == 128
-                and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS):
+                and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS and not geometry_plain_kernels(geo)):
             target = TC_TARGET_CTAS                                       # one CTA of 8 warps per SM
         want = max(1, target // max(1, num_reqs * Hkv))                   # all parts run in one wave
         parts = max(1, min(want, -(-span // FLASH_SPLIT)))
@@ -1067,12 +1087,18 @@ def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) 
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
                     head_dim: int, next_pages: Optional[torch.Tensor] = None,
-                    slopes: Optional[torch.Tensor] = None) -> None:
+                    slopes: Optional[torch.Tensor] = None, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                    value_shift: int = 0) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
     the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
 
     ``slopes`` (float32 [Hq]): the score of query i and key j of head h is scale q.k - slopes[h] (i - j).
+
+    ``softcap`` > 0: the scaled score s becomes softcap tanh(s / softcap).  ``sinks`` (float32 [Hq]): exp(sinks[h])
+    joins the softmax's denominator of head h; it has no key and no value.  ``value_shift`` s: the weights of a head
+    whose kv head is c meet the values of kv head (c + s) mod Hkv (a mixer that mixes the heads' weights sums such
+    outputs).  With any of the three, the mixer's geometry carries the mark of ``geometry_plain_kernels``.
 
     ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
     pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
@@ -1088,7 +1114,15 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     if slopes is not None:
         _need(slopes.dtype == torch.float32 and slopes.numel() == Hq and slopes.is_contiguous(), "paged_attention: slopes must be float32 [Hq]")
     index = plan.get("geometry_index", {})
-    if planes == 1:
+    plain = softcap > 0.0 or sinks is not None or value_shift != 0
+    if sinks is not None:
+        _need(sinks.dtype == torch.float32 and sinks.numel() == Hq and sinks.is_contiguous(), "paged_attention: sinks must be float32 [Hq]")
+    if plain:
+        _need(planes == 2 and slopes is None and 0 <= value_shift < Hkv,
+              "paged_attention: bent scores, sinks and shifted values go with a cache of two planes and no distance bias")
+        key = index.get((Hq, Hkv, D, window, False, 2, True))
+        _need(key is None or f"tc{key}_items" not in plan, "paged_attention: the step's plan sends this mixer to a kernel that does not know its scores")
+    elif planes == 1:
         _need(slopes is None, "paged_attention: no distance bias over a cache of one plane")
         key = index.get((Hq, Hkv, D, window, False, 1))
     else:
@@ -1122,7 +1156,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
-        if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
+        if not plain and _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
             lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
@@ -1145,7 +1179,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), int(small_tiles), ctypes.c_float(scale), int(window),
-            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, _stream()), "flash_attention")
+            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, ctypes.c_float(softcap), _ptr(sinks), int(value_shift),
+            _stream()), "flash_attention")
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2
@@ -1153,7 +1188,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     _check(lib().qe_paged_attention_generic(
         _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
         _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(tiles), n_tiles, _ptr(out), ctypes.c_float(scale), int(window),
-        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _ptr(slopes), planes, _stream()), "paged_attention")
+        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _ptr(slopes), planes, ctypes.c_float(softcap), _ptr(sinks),
+        int(value_shift), _stream()), "paged_attention")
 
 
 def place_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor) -> None:
@@ -1404,7 +1440,7 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: Option
            "delta_rule_scan")
 
 
-ROUTER_SCORINGS = {"softmax_chosen": 0, "softmax_all": 1}
+ROUTER_SCORINGS = {"softmax_chosen": 0, "softmax_all": 1, "sigmoid": 2}
 
 
 def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], top_idx: torch.Tensor, top_w: torch.Tensor,
@@ -1413,7 +1449,8 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], to
     ``softmax_chosen``: the ``top`` largest logits' experts into top_idx int32 [T, top] (the lower index wins a tie)
     and the softmax over those logits alone into top_w float32 [T, top].
     ``softmax_all``: s = softmax(z) over all E outputs; the ``top`` largest of s + correction (float32 [E], optional)
-    are chosen, and their weights are their s as it is (not made to sum to one)."""
+    are chosen, and their weights are their s as it is (not made to sum to one).
+    ``sigmoid``: every output is scored alone, s = sigmoid(z); the ``top`` largest are chosen and their weights are their s."""
     T, W = x.shape
     E = w.shape[0]
     top = top_idx.shape[1]
@@ -1429,13 +1466,15 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], to
 
 
 def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                out: torch.Tensor, activation, alloc, num_identity: int = 0) -> None:
+                out: torch.Tensor, activation, alloc, num_identity: int = 0, weight_inputs: bool = False) -> None:
     """out[t] = sum_j top_w[t, j] * W_down[e] glu(W_gate[e] x[t], W_up[e] x[t]) with e = top_idx[t, j]: the pairs are
     ordered by expert on the device, each expert's rows run as tiles of two grouped products, and the token's choices
     are summed in their order.  w_gate_up [E, 2 I, K] (gate rows, then up rows), w_down [E, N, I]; ``alloc(shape,
     dtype)`` gives scratch memory.  Nothing of the launches depends on the routing.
     ``num_identity``: top_idx may also name E .. E + num_identity - 1, experts without weights whose output is
-    x[t] itself (N = K then); their pairs are ordered behind the others and only the weighted sum looks at them."""
+    x[t] itself (N = K then); their pairs are ordered behind the others and only the weighted sum looks at them.
+    ``weight_inputs``: the weight multiplies what the expert reads, not what it returns: out[t] = sum_j expert_e(top_w[t, j]
+    x[t]).  The first products are linear, so the weight meets their float32 sums ahead of the activation."""
     T, K = x.shape
     E, I2, _ = w_gate_up.shape
     I, N, top = I2 // 2, w_down.shape[1], top_idx.shape[1]
@@ -1444,19 +1483,20 @@ def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_g
           and w_down.shape == (E, N, I) and x.dtype == w_gate_up.dtype == w_down.dtype, "moe_experts: w_gate_up [E, 2 I, K], w_down [E, N, I] in x's dtype")
     _need(out.shape == (T, N) and out.is_contiguous(), "moe_experts: out must be [T, N]")
     _need(num_identity >= 0 and (num_identity == 0 or N == K), "moe_experts: identity experts need outputs of the input's width")
+    _need(not (weight_inputs and num_identity), "moe_experts: weighted inputs and identity experts do not go together")
     offsets = alloc((E + num_identity + 1,), torch.int32)
     sorted_pair = alloc((P,), torch.int32)
     place = alloc((P,), torch.int32)
     _check(lib().qe_moe_sort(_ptr(top_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(place), P, E + num_identity, _stream()), "moe_sort")
     act = alloc((P, I), x.dtype)
     _check(lib().qe_moe_gate_up(_ptr(x), _ptr(w_gate_up), _ptr(offsets), _ptr(sorted_pair), _ptr(act), P, E, I, K, top,
-                                gate_code(activation), _dt(x), _stream()), "moe_gate_up")
+                                gate_code(activation), _dt(x), _ptr(top_w if weight_inputs else None), _stream()), "moe_gate_up")
     # a few rows (decoded tokens): the down product cuts K into shares so that enough CTAs pull the weights; the shares' sums
     # are added, in their order, where the token's choices are
     shares = int(lib().qe_moe_down_shares(P, I, _dt(x)))
     y = alloc((shares, P, N), torch.float32)
     _check(lib().qe_moe_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), P, E, N, I, shares, _dt(x), _stream()), "moe_down")
-    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, shares, _dt(out),
+    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(None if weight_inputs else top_w), _ptr(out), T, N, top, shares, _dt(out),
                                 _ptr(top_idx if num_identity else None), E, _ptr(x if num_identity else None), _dt(x), _stream()),
            "moe_combine")
 
@@ -1581,6 +1621,66 @@ def depth_mix(history: torch.Tensor, weights: torch.Tensor, count: int, out: tor
     _need(weights.dtype == torch.float32 and weights.numel() >= count and weights.is_contiguous(), "depth_mix: weights must be float32 [count]")
     _need(out.shape == history.shape[1:] and out.dtype == torch.float32 and out.is_contiguous(), "depth_mix: out must be float32 [T, W]")
     _check(lib().qe_depth_mix(_ptr(history), _ptr(weights), int(count), _ptr(out), ctypes.c_long(out.numel()), _stream()), "depth_mix")
+
+
+def group_rmsnorm(x: torch.Tensor, rows: Optional[torch.Tensor], weight: torch.Tensor, eps: float, groups: int,
+                  out: torch.Tensor) -> None:
+    """RMS norm in groups: every one of ``groups`` equal consecutive parts of a row is divided by its own
+    sqrt(mean(part^2) + eps), and the whole row is multiplied by ``weight`` (float32 [W]).  out[n] is the norm of row
+    rows[n] of x (of row n without ``rows``); x float32 or the compute type, out float32 or the compute type."""
+    N, W = out.shape
+    _need(x.dim() == 2 and x.shape[1] == W and x.is_contiguous() and out.is_contiguous(), "group_rmsnorm: x and out must be contiguous rows of one width")
+    _need(weight.dtype == torch.float32 and weight.shape == (W,) and weight.is_contiguous(), "group_rmsnorm: weight must be float32 [W]")
+    _need(groups >= 1 and W % groups == 0, f"group_rmsnorm: {W} channels do not split into {groups} equal parts")
+    if rows is not None:
+        _i32(rows, "rows")
+        _need(rows.numel() >= N, "group_rmsnorm: fewer rows than outputs")
+    else:
+        _need(x.shape[0] == N, "group_rmsnorm: x and out must have as many rows")
+    _check(lib().qe_group_rmsnorm(_ptr(x), _dt(x), _ptr(rows), _ptr(weight), ctypes.c_float(eps), int(groups), _ptr(out), _dt(out),
+                                  N, W, _stream()), "group_rmsnorm")
+
+
+def group_norm_add(src: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, dst: torch.Tensor,
+                   next_weight: Optional[torch.Tensor] = None, next_out: Optional[torch.Tensor] = None) -> None:
+    """A sublayer's way back into the float32 stream where its result is normed in groups (see ``group_rmsnorm``):
+    dst[t] = src[t] + norm(branch[t]) * weight; src and dst float32 [T, W] (may be the same), branch float32 or the
+    compute type.  ``next_out`` [T, W] (float32 or the compute type) also gets norm(dst[t]) * next_weight in the same
+    pass: what the sublayer after this one reads."""
+    T, W = src.shape
+    _need(src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous()
+          and dst.shape == (T, W), "group_norm_add: src and dst must be contiguous float32 [T, W]")
+    _need(branch.shape == (T, W) and branch.is_contiguous(), "group_norm_add: branch must be contiguous [T, W]")
+    _need(groups >= 1 and W % groups == 0, f"group_norm_add: {W} channels do not split into {groups} equal parts")
+    for wt in (weight, next_weight):
+        _need(wt is None or (wt.dtype == torch.float32 and wt.shape == (W,) and wt.is_contiguous()), "group_norm_add: weights must be float32 [W]")
+    if next_out is not None:
+        _need(next_weight is not None and next_out.shape == (T, W) and next_out.is_contiguous(), "group_norm_add: next_out must be contiguous [T, W], with its weights")
+    _check(lib().qe_group_norm_add(_ptr(src), _ptr(branch), _dt(branch), _ptr(weight), ctypes.c_float(eps), int(groups), _ptr(dst),
+                                   _ptr(next_weight if next_out is not None else None), _ptr(next_out),
+                                   _dt(next_out) if next_out is not None else 0, T, W, _stream()), "group_norm_add")
+
+
+def head_mix_gate(partial: torch.Tensor, mix: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
+                  num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Attention's heads on their way to the output projection, where a design mixes the heads' attention weights by a
+    matrix ``mix`` (float32 [H, H]) and gates every head by one number.  ``partial`` [S, T, H D]: entry s holds, for
+    every head g, its weights over the values of kv head (c(g) + s) mod Hkv (``paged_attention`` with ``value_shift``
+    s); S = Hkv with ``mix``, else 1.  out[t, h] = sigmoid(gate[t, h]) * sum_g mix[h, g] partial[(c(h) - c(g)) mod Hkv,
+    t, g]; ``gate`` [T, H] in the compute type (rows may be strided), None: no gate; ``mix`` None: partial[0] as it is."""
+    S, T = partial.shape[0], partial.shape[1]
+    H, Hkv, D = num_heads, num_kv_heads, head_dim
+    _need(partial.shape == (S, T, H * D) and partial.is_contiguous() and partial.dtype == out.dtype, "head_mix_gate: partial must be contiguous [S, T, H D] in out's dtype")
+    _need(S == (Hkv if mix is not None else 1), "head_mix_gate: one set of outputs per kv head with a mixing matrix, else one")
+    _need(mix is None or (mix.dtype == torch.float32 and mix.shape == (H, H) and mix.is_contiguous()), "head_mix_gate: mix must be float32 [H, H]")
+    _rows(out, "head_mix_gate: out")
+    _need(out.shape == (T, H * D), "head_mix_gate: out must be [T, H D]")
+    if gate is not None:
+        _rows(gate, "head_mix_gate: gate")
+        _need(gate.shape == (T, H) and gate.dtype == out.dtype, "head_mix_gate: gate must be [T, H] in out's dtype")
+    _check(lib().qe_head_mix_gate(_ptr(partial), ctypes.c_long(T * H * D), S, _ptr(mix), _ptr(gate),
+                                  ctypes.c_long(gate.stride(0) if gate is not None else 0), _ptr(out), ctypes.c_long(out.stride(0)),
+                                  T, H, Hkv, D, _dt(out), _stream()), "head_mix_gate")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -25,6 +25,19 @@ Options that other designs use (all off for Qwen3):
   a q/k norm without weights (``qk_norm_eps`` is its eps), and
   ``query_temperature`` = (coef, every): the query at position p is multiplied by
   1 + coef ln(floor((p + 1) / every) + 1).
+* ``softcap``: the scaled score s becomes softcap * tanh(s / softcap) before the mask and the softmax.
+* ``sink``: one stored number per query head; exp(sink_h) joins head h's softmax denominator.  It has no key and no
+  value, is not scaled and counts once.
+* ``head_mixing``: a stored matrix M [H, H]; head h's attention weights become sum_g M[h, g] weights_g (after the
+  softmax, sink included in the denominators) and meet the values of h's own kv head.  The sum over keys is linear, so
+  the attention kernel runs once per kv-head shift and ``ops.head_mix_gate`` forms the sums over g.
+* ``output_gate`` = "sigmoid_head": every head's output is multiplied by sigmoid(W_g x)_h, one number per head; W_g [H,
+  hidden] rides in the stacked product.
+* ``value_mix``: values shared across layers.  "keep": this layer's values of the step's tokens are kept for the layers
+  after it (``ctx.extras["shared_values"]``); "blend": v <- (1 - lam) v + lam v_kept with the stored scalar lam, and
+  the blended v is what is cached.  The kept values are as projected (the keeping layer blends nothing).
+* a position encoding with ``row_permutation()`` (pairs that the kernels do not rotate as stored): the rows of W_q
+  and W_k are reordered within every head at load; ``magnitude`` multiplies its cosines and sines.
 * ``names``: the tensors' names in the checkpoint.
 """
 from __future__ import annotations
@@ -40,7 +53,7 @@ from .base import Mixer, PartSpec, StepContext, register, step_hint
 
 _NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", out="o_proj.weight",
               q_norm="q_norm.weight", k_norm="k_norm.weight", gate="g_proj.weight",
-              q_bias="q_proj.bias", k_bias="k_proj.bias")
+              q_bias="q_proj.bias", k_bias="k_proj.bias", sink="sinks", head_mix="head_mix", value_mix="value_mix")
 
 
 def _pad_rows(w: torch.Tensor, heads: int, dim: int, padded: int) -> torch.Tensor:
@@ -61,10 +74,11 @@ class GQAAttention(Mixer):
                  position_encoding: Optional[PartSpec] = None, window: Optional[int] = None,
                  value_dim: Optional[int] = None, distance_slopes=None, output_gate: Optional[str] = None,
                  names: Optional[dict] = None, tied_values: bool = False, qk_bias: bool = False,
-                 query_temperature=None):
+                 query_temperature=None, softcap: Optional[float] = None, sink: bool = False, head_mixing: bool = False,
+                 value_mix: Optional[str] = None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if output_gate not in (None, "sigmoid"):
+        if output_gate not in (None, "sigmoid", "sigmoid_head"):
             raise ValueError(f"unknown output gate {output_gate!r}")
         if distance_slopes is not None and len(distance_slopes) != num_heads:
             raise ValueError("one distance slope per query head")
@@ -94,11 +108,32 @@ class GQAAttention(Mixer):
             raise ValueError("q/k biases and a query temperature come with values that are the keys")
         self.distance_slopes = None if distance_slopes is None else tuple(float(x) for x in distance_slopes)
         self.names = dict(_NAMES, **(names or {}))
+        if value_mix not in (None, "keep", "blend"):
+            raise ValueError(f"unknown value_mix {value_mix!r}")
+        self.softcap = None if not softcap else float(softcap)
+        self.sink, self.head_mixing, self.value_mix = bool(sink), bool(head_mixing), value_mix
+        # scores or values that only the flash and the generic kernel know
+        self.plain_kernels = bool(self.softcap or self.sink or self.head_mixing)
+        self.per_head = bool(self.plain_kernels or value_mix or output_gate == "sigmoid_head"
+                             or getattr(self.pos, "row_permutation", None) is not None)
+        if self.per_head and (self.tied_values or self.distance_slopes is not None or window or qk_norm_eps is not None):
+            raise ValueError("bent scores, sinks, mixed heads, shared values and a gate per head go without a window, a distance "
+                             "bias, a q/k norm or tied values")
+        if self.per_head and output_gate == "sigmoid":
+            raise ValueError("with these options the output gate is one number per head ('sigmoid_head') or absent")
+        if self.per_head and self.pos is not None and self.pos.half_split_rotation() is None:
+            raise ValueError("these options rotate q and k inside the kernel that writes the cache")
+        self.gate_width = 0
+        if output_gate == "sigmoid_head":
+            self.gate_width = -(-num_heads // 8) * 8        # padded with zero rows, so that the stacked product's rows stay aligned
+        self.sinks = self.head_mix = self.mix_lambda = None
         # the step takes the route of separate operations (one stacked product, norm and cache write, attention, gate,
         # output product) when any of the options above is on
-        self.extended = bool(output_gate or self.distance_slopes is not None or self.value_dim != self.key_dim or self.tied_values)
+        self.extended = bool(output_gate or self.distance_slopes is not None or self.value_dim != self.key_dim or self.tied_values
+                             or self.per_head)
         self.inner_width = self.q_width
-        self.input_width = self.q_width + (1 if self.tied_values else 2) * self.kv_width + (self.q_width if output_gate else 0)
+        self.input_width = (self.q_width + (1 if self.tied_values else 2) * self.kv_width
+                            + (self.gate_width if output_gate == "sigmoid_head" else self.q_width if output_gate else 0))
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.slopes = self.q_bias = self.k_bias = None
 
     def cache_spec(self):
@@ -106,6 +141,8 @@ class GQAAttention(Mixer):
 
     def attention_geometry(self):
         geo = (self.num_heads, self.num_kv_heads, self.head_dim, self.window or 0)
+        if self.plain_kernels:
+            return geo + (False, 2, True)
         return geo + (True,) if self.distance_slopes is not None else geo
 
     def weight_specs(self, prefix: str) -> list[WeightSpec]:
@@ -117,8 +154,17 @@ class GQAAttention(Mixer):
         if not self.tied_values:
             specs.append(WeightSpec(prefix + n["v"], (G * self.value_dim, W), MATRIX))
         specs.append(WeightSpec(prefix + n["out"], (W, H * self.value_dim), MATRIX))
-        if self.output_gate:
+        if self.output_gate == "sigmoid_head":
+            specs.append(WeightSpec(prefix + n["gate"], (H, W), MATRIX))
+        elif self.output_gate:
             specs.append(WeightSpec(prefix + n["gate"], (H * self.value_dim, W), MATRIX))
+        if self.sink:
+            specs.append(WeightSpec(prefix + n["sink"], (H,), VECTOR))
+        if self.head_mixing:
+            specs.append(WeightSpec(prefix + n["head_mix"], (H, H), MATRIX))
+        if self.value_mix:
+            # (the keeping layer's scalar is stored and not used)
+            specs.append(WeightSpec(prefix + n["value_mix"], (), VECTOR, optional=self.value_mix == "keep"))
         if self.qk_bias:
             specs += [WeightSpec(prefix + n["q_bias"], (H * self.key_dim,), VECTOR),
                       WeightSpec(prefix + n["k_bias"], (G * self.key_dim,), VECTOR)]
@@ -132,12 +178,28 @@ class GQAAttention(Mixer):
     def load(self, prefix, source, dtype, device) -> None:
         n, H, G, D = self.names, self.num_heads, self.num_kv_heads, self.head_dim
         # q, k and v rows stacked (and the gate's behind them): one product gives [T, q_width + 2 kv_width (+ q_width)]
-        rows = [_pad_rows(source.get(prefix + n["q"]), H, self.key_dim, D),
-                _pad_rows(source.get(prefix + n["k"]), G, self.key_dim, D)]
+        perm = getattr(self.pos, "row_permutation", lambda: None)() if self.pos is not None else None
+
+        def qk_rows(name, heads):
+            w = source.get(prefix + name)
+            if perm is not None:                     # the same reordering of q's and k's channels leaves every q.k as it was
+                w = w.reshape(heads, self.key_dim, w.shape[1])[:, perm].reshape(heads * self.key_dim, w.shape[1])
+            return _pad_rows(w, heads, self.key_dim, D)
+
+        rows = [qk_rows(n["q"], H), qk_rows(n["k"], G)]
         if not self.tied_values:
             rows.append(_pad_rows(source.get(prefix + n["v"]), G, self.value_dim, D))
-        if self.output_gate:
+        if self.output_gate == "sigmoid_head":
+            w_g = source.get(prefix + n["gate"])
+            rows.append(torch.cat([w_g, w_g.new_zeros((self.gate_width - H, w_g.shape[1]))], dim=0))
+        elif self.output_gate:
             rows.append(_pad_rows(source.get(prefix + n["gate"]), H, self.value_dim, D))
+        if self.sink:
+            self.sinks = source.get(prefix + n["sink"]).to(torch.float32).to(device).contiguous()
+        if self.head_mixing:
+            self.head_mix = source.get(prefix + n["head_mix"]).to(torch.float32).to(device).contiguous()
+        if self.value_mix == "blend":
+            self.mix_lambda = float(source.get(prefix + n["value_mix"]).to(torch.float32))
         self.w_qkv = ops.prepare_matrix(torch.cat(rows, dim=0).to(dtype).to(device))
         w_o = source.get(prefix + n["out"])
         if self.value_dim != D:                      # zero columns where the attention's output is padding
@@ -188,6 +250,9 @@ class GQAAttention(Mixer):
             return
         n_qkv = self.q_width + 2 * self.kv_width
         qkv = proj[:, :n_qkv]
+        if self.per_head:
+            self._mix_per_head(ctx, proj, qkv, cache, view, inner, write_cache, scale)
+            return
         if self.pos is not None:
             # norm, then the part's own rotation, then the plain cache write (the order of model.py:204-208)
             ops.qk_norm_rope_kv_write(qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, None, 0,
@@ -206,6 +271,39 @@ class GQAAttention(Mixer):
         if attn is not inner:
             ops.head_norm_gate(attn, proj[:, n_qkv:n_qkv + self.q_width] if self.output_gate else None, None, 0.0, inner, H, D,
                                gate_kind=self.output_gate, scale=scale)
+
+    def _mix_per_head(self, ctx: StepContext, proj, qkv, cache, view, inner, write_cache: bool, scale: float) -> None:
+        """Rotation (inside the kernel that blends and writes the cache), attention with bent scores or a sink, the heads'
+        weights mixed, a gate per head."""
+        T = ctx.num_tokens
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if scale != 1.0:
+            raise NotImplementedError("gqa_attention: no output scale with these options")
+        shared = None
+        if self.value_mix:
+            first = step_hint(ctx, "shared_values")
+            if self.value_mix == "keep":
+                first = ctx.arena.alloc_step((T, self.kv_width), ctx.dtype)
+                ctx.extras["shared_values"] = first
+                shared = ("keep", first)
+            else:
+                if first is None or first.shape != (T, self.kv_width):
+                    raise RuntimeError("gqa_attention: values to blend with, but no layer before this one kept its own")
+                shared = ("blend", first, self.mix_lambda)
+        rot = self.pos.half_split_rotation() if self.pos is not None else None
+        ops.qk_norm_rope_kv_write(qkv, ctx.positions, None, None, 0.0, rot.inv_freq if rot is not None else None,
+                                  rot.rotary_dim if rot is not None else 0, cache, view.slot_mapping, H, Hkv, D,
+                                  write_kv=write_cache, magnitude=getattr(rot, "magnitude", 1.0) if rot is not None else 1.0,
+                                  value_mix=shared)
+        shifts = Hkv if self.head_mixing else 1
+        gate = proj[:, self.q_width + 2 * self.kv_width:self.q_width + 2 * self.kv_width + H] if self.output_gate else None
+        direct = shifts == 1 and gate is None and inner.is_contiguous()
+        partial = inner.unsqueeze(0) if direct else ctx.arena.alloc((shifts, T, self.q_width), ctx.dtype)
+        for s in range(shifts):
+            ops.paged_attention(qkv, cache, view.block_tables, ctx, partial[s], self.scale, 0, H, Hkv, D,
+                                softcap=self.softcap or 0.0, sinks=self.sinks, value_shift=s)
+        if not direct:
+            ops.head_mix_gate(partial, self.head_mix, gate, inner, H, Hkv, D)
 
     def forward(self, ctx: StepContext, x, cache, group, out, write_cache: bool = True) -> None:
         T = ctx.num_tokens

@@ -322,6 +322,12 @@ class Block(Part):
         per request (``forward`` gets the caches and groups in this order)."""
         return self.mixer.cache_specs()
 
+    def first_norm(self):
+        """None, or (the norm part that reads the stream first, the type its reader wants or None for the compute type):
+        the block that runs before this one may then form that norm in its last add and leave the rows in
+        ``ctx.extras["normed_ahead"]`` as (the norm part, the rows)."""
+        return None
+
     def forward(self, ctx: StepContext, stream, cache: Optional[torch.Tensor], group: Optional[int],
                 write_cache: bool) -> None:
         """Run the layer on the residual stream (an ``ops.ResidualStream``: the float32 stream, and

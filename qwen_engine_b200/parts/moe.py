@@ -11,6 +11,10 @@ epilogue.  Nothing of the launches depends on the routing, so steps are replayed
 ``scoring`` = "softmax_all": s = softmax(z) over all router outputs; the `top` largest of s + correction (a stored
 vector) are chosen and their weights are their s as it is.  ``num_identity``: the router's last outputs stand for
 experts without weights that hand their input on (times the weight).  ``router_bias_name`` None: no router bias.
+
+``scoring`` = "sigmoid": every router output is scored alone, s = sigmoid(z); the `top` largest are chosen and their
+weights are their s, not made to sum to one.  ``weight_inputs``: the weight multiplies what an expert reads, not what it
+returns: out = sum over the chosen e of expert_e(weight_e * h).
 """
 from __future__ import annotations
 
@@ -28,7 +32,7 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, activation="silu",
                  names: tuple = ("gate", "up", "down"), router_name: str = "router", router_bias_name: Optional[str] = "router.b",
                  expert_prefix: str = "e", scoring: str = "softmax_chosen", correction_name: Optional[str] = None,
-                 num_identity: int = 0):
+                 num_identity: int = 0, weight_inputs: bool = False):
         if not ops.gate_activation_known(activation):
             raise ValueError(f"unknown activation {activation!r}")
         if not (1 <= top <= num_experts + num_identity):
@@ -37,6 +41,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"unknown scoring {scoring!r}, or a correction without scores over all experts")
         self.scoring, self.correction_name, self.num_identity = scoring, correction_name, int(num_identity)
         self.correction = None
+        self.weight_inputs = bool(weight_inputs)
+        if self.weight_inputs and num_identity:
+            raise ValueError("weighted inputs and identity experts do not go together")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top = num_experts, top
         self.activation = tuple(activation) if isinstance(activation, (tuple, list)) else activation
@@ -83,4 +90,4 @@ class RoutedExperts(FeedForward):
         top_w = ctx.arena.alloc((T, self.top), torch.float32)
         ops.moe_route(x, self.w_router, self.router_bias, top_idx, top_w, scoring=self.scoring, correction=self.correction)
         ops.moe_experts(x, top_idx, top_w, self.w_gate_up, self.w_down, out, self.activation, ctx.arena.alloc,
-                        num_identity=self.num_identity)
+                        num_identity=self.num_identity, weight_inputs=self.weight_inputs)

@@ -11,11 +11,12 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .config import BesavikConfig, ConfigError, GanidraConfig, MerudraConfig, ModelConfig, Qwen3Config, read_config_json
+from .config import BesavikConfig, ConfigError, GanidraConfig, MerudraConfig, ModelConfig, PufivikConfig, Qwen3Config, read_config_json
 from .models.decoder import DecoderModel, ModelLayout
 from .models.besavik import besavik_layout
 from .models.ganidra import ganidra_layout
 from .models.merudra import merudra_layout
+from .models.pufivik import pufivik_layout
 from .models.qwen3 import qwen3_layout
 
 
@@ -37,6 +38,7 @@ register_architecture("Qwen3ForCausalLM", Qwen3Config, qwen3_layout)
 register_architecture("Ganidra", GanidraConfig, ganidra_layout)
 register_architecture("Besavik", BesavikConfig, besavik_layout)
 register_architecture("Merudra", MerudraConfig, merudra_layout)
+register_architecture("Pufivik", PufivikConfig, pufivik_layout)
 
 
 def architecture_of(raw_config: dict[str, Any]) -> Architecture:

@@ -64,10 +64,10 @@ def linear(x, w, out):
     out.copy_((x.to(torch.float32) @ w.to(torch.float32).t()).to(out.dtype))
 
 
-def _rotate(x, positions, inv_freq, rotary_dim):
+def _rotate(x, positions, inv_freq, rotary_dim, magnitude=1.0):
     """x [T, heads, D] float32 -> rotated copy (half-split pairs over the first rotary_dim dims)."""
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
-    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    c, s = torch.cos(ang)[:, None, :] * magnitude, torch.sin(ang)[:, None, :] * magnitude
     half = rotary_dim // 2
     x1, x2 = x[..., :half], x[..., half:rotary_dim]
     return torch.cat([c * x1 - s * x2, s * x1 + c * x2, x[..., rotary_dim:]], dim=-1)
@@ -87,7 +87,8 @@ def rope_table(positions, inv_freq, out):
 
 
 def qk_norm_rope_kv_write(qkv, positions, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, kv_pages,
-                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True, cos_sin=None, norm_dim=None):
+                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True, cos_sin=None, norm_dim=None,
+                          magnitude=1.0, value_mix=None):
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     q = qkv[:, :Hq * D].reshape(T, Hq, D).to(torch.float32)
@@ -99,8 +100,14 @@ def qk_norm_rope_kv_write(qkv, positions, q_norm_w, k_norm_w, eps, inv_freq, rot
     if k_norm_w is not None:
         k = k * torch.rsqrt((k * k).sum(dim=-1, keepdim=True) / n + eps) * k_norm_w
     if inv_freq is not None:
-        q = _rotate(q, positions, inv_freq, rotary_dim)
-        k = _rotate(k, positions, inv_freq, rotary_dim)
+        q = _rotate(q, positions, inv_freq, rotary_dim, magnitude)
+        k = _rotate(k, positions, inv_freq, rotary_dim, magnitude)
+    if value_mix is not None:
+        if value_mix[0] == "keep":
+            value_mix[1].copy_(v.reshape(T, Hkv * D))
+        else:
+            lam = float(value_mix[2])
+            v = ((1.0 - lam) * v.to(torch.float32) + lam * value_mix[1].reshape(T, Hkv, D).to(torch.float32)).to(qkv.dtype)
     qkv[:, :Hq * D] = q.reshape(T, Hq * D).to(qkv.dtype)
     qkv[:, Hq * D:(Hq + Hkv) * D] = k.reshape(T, Hkv * D).to(qkv.dtype)
     if write_kv:
@@ -125,7 +132,7 @@ def plan_attention(q_lens, ctx_lens, page_size, geometries=(), dtype=None, unifo
 
 
 def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim, next_pages=None,
-                    slopes=None):
+                    slopes=None, softcap=0.0, sinks=None, value_shift=0):
     """For each request: gather its keys and values from the pages by its block table, then
     softmax(scale q k^T + mask) v with key j allowed for the query at position i iff
     j <= i and (window == 0 or j > i - window)."""
@@ -160,9 +167,14 @@ def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_he
             s = (q[:, h, :] @ k[:, h // group, :].t()) * scale
             if slopes is not None:
                 s = s - float(slopes[h]) * (qpos[:, None] - kpos[None, :]).to(torch.float32)
+            if softcap and softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
             s = s.masked_fill(~allowed, float("-inf"))
-            p = torch.softmax(s, dim=-1)
-            out[a:b, h * D:(h + 1) * D] = (p @ v[:, h // group, :]).to(out.dtype)
+            if sinks is not None:
+                p = torch.softmax(torch.cat([s, sinks[h].reshape(1, 1).expand(n, 1)], dim=-1), dim=-1)[:, :-1]
+            else:
+                p = torch.softmax(s, dim=-1)
+            out[a:b, h * D:(h + 1) * D] = (p @ v[:, (h // group + value_shift) % Hkv, :]).to(out.dtype)
 
 
 def silu_mul(gate_up, out):
@@ -337,10 +349,10 @@ def moe_route(x, w, bias, top_idx, top_w, scoring="softmax_chosen", correction=N
         return
     val, idx = torch.topk(z, top_idx.shape[1], dim=-1)
     top_idx.copy_(idx.to(torch.int32))
-    top_w.copy_(torch.softmax(val, dim=-1))
+    top_w.copy_(torch.sigmoid(val) if scoring == "sigmoid" else torch.softmax(val, dim=-1))
 
 
-def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc, num_identity=0):
+def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc, num_identity=0, weight_inputs=False):
     T = x.shape[0]
     E = w_gate_up.shape[0]
     I = w_gate_up.shape[1] // 2
@@ -352,10 +364,13 @@ def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc, nu
                 assert e < E + num_identity
                 acc[t] += float(top_w[t, j]) * x[t].to(torch.float32)
                 continue
-            gu = (x[t:t + 1].to(torch.float32) @ w_gate_up[e].to(torch.float32).t()).to(x.dtype)
+            gu = x[t:t + 1].to(torch.float32) @ w_gate_up[e].to(torch.float32).t()
+            if weight_inputs:                # the weight meets the first products' sums ahead of the activation
+                gu = gu * float(top_w[t, j])
+            gu = gu.to(x.dtype)
             act = torch.empty(1, I, dtype=x.dtype)
             act_mul(gu, act, activation)
-            acc[t] += float(top_w[t, j]) * (act.to(torch.float32) @ w_down[e].to(torch.float32).t())[0]
+            acc[t] += (1.0 if weight_inputs else float(top_w[t, j])) * (act.to(torch.float32) @ w_down[e].to(torch.float32).t())[0]
     out.copy_(acc.to(out.dtype))
 
 
@@ -425,6 +440,43 @@ def gated_norm_add(src, branch, gate, gate_bias, weight, eps, dst, dst_cast=None
         history, weights, count, mixed = depth_mix
         assert dst.data_ptr() == history[count - 1].data_ptr()
         globals()["depth_mix"](history, weights, count, mixed)
+
+
+def _group_rms(x, weight, eps, groups):
+    x = x.to(torch.float32)
+    n, W = x.shape
+    parts = x.reshape(n, groups, W // groups)
+    parts = parts / torch.sqrt((parts * parts).mean(dim=-1, keepdim=True) + eps)
+    return parts.reshape(n, W) * weight
+
+
+def group_rmsnorm(x, rows, weight, eps, groups, out):
+    src = x if rows is None else x[rows[:out.shape[0]].long()]
+    out.copy_(_group_rms(src, weight, eps, groups).to(out.dtype))
+
+
+def group_norm_add(src, branch, weight, eps, groups, dst, next_weight=None, next_out=None):
+    res = src + _group_rms(branch, weight, eps, groups)
+    dst.copy_(res)
+    if next_out is not None:
+        next_out.copy_(_group_rms(res, next_weight, eps, groups).to(next_out.dtype))
+
+
+def head_mix_gate(partial, mix, gate, out, num_heads, num_kv_heads, head_dim):
+    S, T = partial.shape[0], partial.shape[1]
+    H, Hkv, D = num_heads, num_kv_heads, head_dim
+    G = H // Hkv
+    p = partial.to(torch.float32).reshape(S, T, H, D)
+    if mix is None:
+        res = p[0].clone()
+    else:
+        res = torch.zeros(T, H, D, dtype=torch.float32)
+        for h in range(H):
+            for g in range(H):
+                res[:, h] += mix[h, g] * p[(h // G - g // G) % Hkv, :, g]
+    if gate is not None:
+        res = res * torch.sigmoid(gate.to(torch.float32))[:, :, None]
+    out.copy_(res.reshape(T, H * D).to(out.dtype))
 
 
 def token_side_gate(gate, table, token_ids, out):
@@ -499,7 +551,7 @@ def copy_pages(cache, pairs):
         cache[:, dst] = cache[:, src].clone()
 
 
-_NAMES = ["qk_bias_norm_kv_write", "stream_conv", "gated_norm_add", "token_side_gate", "depth_mix", "latent_prepare", "head_linear", "short_conv", "unit_norm", "delta_rule_scan", "moe_route", "moe_experts",
+_NAMES = ["group_rmsnorm", "group_norm_add", "head_mix_gate", "qk_bias_norm_kv_write", "stream_conv", "gated_norm_add", "token_side_gate", "depth_mix", "latent_prepare", "head_linear", "short_conv", "unit_norm", "delta_rule_scan", "moe_route", "moe_experts",
           "act_mul", "channel_decay", "linear_attention_scan", "head_norm_gate", "scaled_add", "copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
