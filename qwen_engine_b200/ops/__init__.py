@@ -827,6 +827,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
               and kv_pages.shape[1] == 2 and kv_pages.shape[2] == Hkv and kv_pages.shape[4] == D,
               "qk_norm_rope_kv_write: kv_pages must be [pages, 2, Hkv, page, D] in qkv's dtype")
         _i32(slot_mapping, "slot_mapping")
+        _need(slot_mapping.numel() >= T, "qk_norm_rope_kv_write: one cache slot per token")
         page_size = kv_pages.shape[3]
     for wt in (q_norm_w, k_norm_w):
         if wt is not None:
@@ -1127,6 +1128,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         key = index.get((Hq, Hkv, D, window, False, 1))
     else:
         key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
+        if key is None and slopes is None:
+            key = index.get((Hq, Hkv, D, window, False, 2, True))      # (a mixer that is marked for the plain kernels and uses none of their options)
     if key is not None and f"tc{key}_items" in plan:
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]

@@ -46,8 +46,10 @@ def base_frequencies(rot):
 def banded_frequencies(rot):
     """Frequencies whose wavelength is short stay, those whose wavelength is long are divided by ``factor``, and those
     between the two bands (``original / high`` and ``original / low``) are blended.  Returns (frequencies, 1.0)."""
-    s = rot["scaling"]
+    s = rot.get("scaling")
     f = base_frequencies(rot)
+    if s is None:
+        return f, 1.0
     out = f.clone()
     for i, fi in enumerate(f.tolist()):
         wavelength = 2.0 * math.pi / fi
@@ -65,9 +67,11 @@ def ramped_frequencies(rot):
     """Frequencies blended between f and f / factor along a ramp over the pair index, whose ends are the indices at
     which ``fast`` and ``slow`` turns fit into ``original`` positions; cosines and sines grow by 0.1 ln(factor) + 1.
     Returns (frequencies, magnitude)."""
-    s = rot["scaling"]
+    s = rot.get("scaling")
     dims, base = rot["dims"], rot["base"]
     f = base_frequencies(rot)
+    if s is None:
+        return f, 1.0
 
     def index_of(turns):
         return dims * math.log(s["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
@@ -160,11 +164,17 @@ def capped_attention(h, w, p, m, shared, positions=None):
     return out.reshape(T, H * Dv) @ w[p + "o"].T
 
 
-def input_weighted_experts(h, w, p, mlp):
-    """Sigmoid scores; the ``top`` largest are chosen; an expert reads its score times h."""
+def input_weighted_experts(h, w, p, mlp, margins=None):
+    """Sigmoid scores; the ``top`` largest are chosen; an expert reads its score times h.  ``margins`` (a list) gets, per
+    token, by how much the last chosen router logit leads the first one left out (inf when all are chosen)."""
     r = mlp["router"]
-    scores = torch.sigmoid(h @ w[p + "router"].T)
+    z = h @ w[p + "router"].T
+    scores = torch.sigmoid(z)
     chosen = torch.topk(scores, r["top"], dim=-1).indices
+    if margins is not None:
+        ordered = torch.sort(z, dim=-1, descending=True).values
+        margins.append(ordered[:, r["top"] - 1] - ordered[:, r["top"]] if r["top"] < z.shape[1]
+                       else torch.full((h.shape[0],), math.inf, dtype=F64))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -177,7 +187,7 @@ def input_weighted_experts(h, w, p, mlp):
 MIXERS = {"attention": sink_talking_attention, "attention_2": capped_attention}
 
 
-def forward(cfg: dict, weights: dict, token_ids, return_layers: bool = False):
+def forward(cfg: dict, weights: dict, token_ids, return_layers: bool = False, margins=None):
     """Logits [T, vocab] of one sequence from its first token on."""
     w = {k: v.to(F64) for k, v in weights.items()}
     eps, groups, mult = cfg["norm"]["eps"], cfg["norm"]["groups"], cfg["residual_mult"]
@@ -193,7 +203,7 @@ def forward(cfg: dict, weights: dict, token_ids, return_layers: bool = False):
         x = x + mult * group_rms_norm(y, w[p + "norm1b"], groups, eps)
         if layer.get("mlp") is not None:
             h = group_rms_norm(x, w[p + "norm2"], groups, eps)
-            y = input_weighted_experts(h, w, p + "mlp.", layer["mlp"])
+            y = input_weighted_experts(h, w, p + "mlp.", layer["mlp"], margins)
             x = x + mult * group_rms_norm(y, w[p + "norm2b"], groups, eps)
         after.append(x)
     logits = group_rms_norm(x, w["final.norm"], groups, eps) @ w["embed"].T
