@@ -463,7 +463,7 @@ _TIMED_OPS = ("embedding", "linear", "linear_swiglu", "linear_swiglu_small", "li
               "qk_norm_rope_kv_write", "paged_attention", "channel_decay", "linear_attention_scan", "head_norm_gate",
               "add_rmsnorm", "add_rmsnorm_rows", "rope_table", "latent_prepare", "head_linear", "short_conv", "unit_norm",
               "delta_rule_scan", "moe_route", "moe_experts", "qk_bias_norm_kv_write", "stream_conv", "gated_norm_add",
-              "token_side_gate", "depth_mix")
+              "token_side_gate", "depth_mix", "group_rmsnorm", "group_norm_add", "head_mix_gate")
 
 
 def ganidra_config_of(sz: dict) -> dict:
@@ -509,6 +509,133 @@ def merudra_config_of(sz: dict) -> dict:
             dict(type="delta", mixer=delta, mlp=moe), dict(type="attention", mixer=attn, mlp=moe)]
     return dict(architecture="Merudra", vocab=sz["vocab"], width=sz["width"], norm=dict(eps=1e-6), canon=dict(taps=4),
                 token_side=dict(dim=64), layers=four * (sz["layers"] // 4))
+
+
+def pufivik_config_of(sz: dict) -> dict:
+    """A Pufivik model at the sizes of ``sz``: three layers of attention with bent scores and one with a sink, mixed heads
+    and a gate per head, twice over; half of every head rotated, with scaled frequencies; values blended with the first
+    layer's; behind every mixer eight experts of half the dense feed-forward's width, two per token, scored by sigmoids;
+    norms in four groups around every sublayer; the mixers read their input through convolutions of four taps."""
+    D = sz["head_dim"]
+    common = dict(heads=sz["heads"], kv_heads=sz["kv_heads"], dim=D, vdim=D, scale=D ** -0.5, v_mix=True)
+    capped = dict(common, softcap=30.0, rot=dict(base=1000000.0, dims=D // 2, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
+    sunk = dict(common, rot=dict(base=500000.0, dims=D // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2), router=dict(experts=8, top=2))
+    four = [dict(type="attention_2", mixer=capped, mlp=moe), dict(type="attention_2", mixer=capped, mlp=moe),
+            dict(type="attention_2", mixer=capped, mlp=moe), dict(type="attention", mixer=sunk, mlp=moe)]
+    return dict(architecture="Pufivik", vocab=sz["vocab"], width=sz["width"], norm=dict(eps=1e-6, groups=4), canon=dict(taps=4),
+                embedding=dict(scale=1.0), residual_mult=0.5, layers=four * (sz["layers"] // 4))
+
+
+def pufivik_kernels_alone(torch, ops, peaks) -> dict:
+    """The kernels and kernel options that Pufivik adds, each alone on rows that do not fit in L2 (16 384 tokens of width
+    2 048: a float32 stream of 134 MB), beside the like kernel of the other models on the same rows: device time (CUDA
+    events, ten launches after three), the bytes the operation has to move, and their rate over the measured copy rate;
+    for attention the multiply-adds over the time instead."""
+    from types import SimpleNamespace
+    from qwen_engine_b200.engine.runner import ModelRunner
+    from qwen_engine_b200.parts.base import Arena
+    dev, bf, f32 = "cuda:0", torch.bfloat16, torch.float32
+    T, W, reqs = 16384, 2048, 8
+    hbm = float(peaks["hbm_gbs"])
+    g = torch.Generator(device=dev).manual_seed(5)
+    rnd = lambda *shape, dtype=f32, std=1.0: (torch.randn(*shape, device=dev, dtype=f32, generator=g) * std).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    per = T // reqs
+    out: dict = {}
+
+    def timed(name, fn, nbytes, like=None, flops=None):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 100.0
+        out[name] = {"us": round(us, 1), "mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / us / 1e3, 1),
+                     "frac_of_copy": round(nbytes / us / 1e3 / hbm, 3)}
+        if flops:
+            out[name]["tflops"] = round(flops / us / 1e6, 1)
+        if like:
+            out[name]["like"] = like
+
+    n = T * W
+    stream, stream2 = rnd(T, W), rnd(T, W)
+    branch, cast, cast32 = rnd(T, W, dtype=bf), torch.empty(T, W, device=dev, dtype=bf), torch.empty(T, W, device=dev, dtype=f32)
+    wt, wt2 = rnd(W) + 1.0, rnd(W) + 1.0
+    timed("add_rmsnorm", lambda: ops.add_rmsnorm(stream, branch, wt, 1e-6, cast), n * 12)
+    timed("group_rmsnorm into the compute type", lambda: ops.group_rmsnorm(stream, None, wt, 1e-6, 4, cast), n * 6, like="add_rmsnorm")
+    timed("group_rmsnorm into float32", lambda: ops.group_rmsnorm(stream, None, wt, 1e-6, 4, cast32), n * 8, like="add_rmsnorm")
+    timed("group_norm_add", lambda: ops.group_norm_add(stream, branch, wt, 1e-6, 4, stream2), n * 10, like="add_rmsnorm, gated_norm_add")
+    timed("group_norm_add with the next norm (compute type)", lambda: ops.group_norm_add(stream, branch, wt, 1e-6, 4, stream2, wt2, cast),
+          n * 12, like="add_rmsnorm, gated_norm_add")
+    timed("group_norm_add with the next norm (float32)", lambda: ops.group_norm_add(stream, branch, wt, 1e-6, 4, stream2, wt2, cast32),
+          n * 14, like="add_rmsnorm, gated_norm_add")
+    timed("gated_norm_add without gate", lambda: ops.gated_norm_add(stream, branch, None, None, wt, 1e-6, stream2), n * 10)
+    del stream2, cast32, branch
+    Hq, Hkv, D, page = 16, 8, 128, 16
+    pos = torch.arange(T, device=dev, dtype=torch.int32) % per
+    slots = torch.arange(T, device=dev, dtype=torch.int32)
+    pages = rnd(T // page, 2, Hkv, page, D, dtype=bf)
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=bf)
+    nw = rnd(D) + 1.0
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=dev, dtype=f32) / D))
+    inv_half = inv[:D // 4].contiguous()
+    first = rnd(T, Hkv * D, dtype=bf)
+    moved = T * ((Hq + Hkv) * D * 2 * 2 + Hkv * D * 2 + 2 * Hkv * D * 2)
+    timed("qk_norm_rope_kv_write", lambda: ops.qk_norm_rope_kv_write(qkv, pos, nw, nw, 1e-6, inv, D, pages, slots, Hq, Hkv, D), moved)
+    timed("rotation of half a head with a magnitude, values blended, cache write",
+          lambda: ops.qk_norm_rope_kv_write(qkv, pos, None, None, 0.0, inv_half, D // 2, pages, slots, Hq, Hkv, D, magnitude=1.14,
+                                            value_mix=("blend", first, 0.3)), moved + T * Hkv * D * 2, like="qk_norm_rope_kv_write")
+    E, top = 8, 2
+    rx, rw = rnd(T, W, dtype=bf), rnd(E, W, std=0.05)
+    ti, tw = torch.empty(T, top, device=dev, dtype=torch.int32), torch.empty(T, top, device=dev, dtype=f32)
+    timed("moe_route by sigmoids", lambda: ops.moe_route(rx, rw, None, ti, tw, "sigmoid"), n * 2, like="moe_route over the chosen")
+    timed("moe_route over the chosen", lambda: ops.moe_route(rx, rw, None, ti, tw, "softmax_chosen"), n * 2)
+    del rx
+    partial = rnd(Hkv, T // 4, Hq * D, dtype=bf)
+    mix = rnd(Hq, Hq)
+    inner = torch.empty(T // 4, Hq * D, device=dev, dtype=bf)
+    gate_rows = rnd(T // 4, 16, dtype=bf)
+    timed("head_mix_gate over eight kv heads", lambda: ops.head_mix_gate(partial, mix, gate_rows, inner, Hq, Hkv, D),
+          (T // 4) * Hq * D * 2 * (Hkv + 1), like="head_norm_gate")
+    one = partial[:1].contiguous()
+    timed("head_mix_gate, the gate alone", lambda: ops.head_mix_gate(one, None, gate_rows, inner, Hq, Hkv, D), (T // 4) * Hq * D * 4, like="head_norm_gate")
+    full_gate = rnd(T // 4, Hq * D, dtype=bf)
+    timed("head_norm_gate", lambda: ops.head_norm_gate(one[0], full_gate, None, 0.0, inner, Hq, D, gate_kind="sigmoid"), (T // 4) * Hq * D * 6)
+    del partial, one, full_gate
+    # attention: eight prompts of 2 048 tokens; the same rows through the tcgen05 kernel (the other models' route at this
+    # head size), the flash kernel as it was, and the flash kernel with bent scores and with a sink
+    q_lens, ctx_lens = [per] * reqs, [0] * reqs
+    blocks = per // page
+    tables = torch.arange(reqs * blocks, device=dev, dtype=torch.int32).view(reqs, blocks).contiguous()
+    attn_out = torch.empty(T, Hq * D, device=dev, dtype=bf)
+    sinks = rnd(Hq)
+    macs = reqs * Hq * D * 2 * (per * (per + 1) // 2)              # q.k and p.v over the allowed pairs
+    cu = [r * per for r in range(reqs + 1)]
+    geo = (Hq, Hkv, D, 0)
+    for label, flash, kw in (("paged_attention, tcgen05 kernel", False, {}),
+                             ("paged_attention, tcgen05 kernel, bent scores", False, dict(softcap=30.0)),
+                             ("paged_attention, tcgen05 kernel, sink and values of the next kv head", False, dict(sinks=sinks, value_shift=1)),
+                             ("paged_attention, flash kernel", True, {}),
+                             ("paged_attention, flash kernel, bent scores", True, dict(softcap=30.0))):
+        saved = ops.TC_MIN_ROWS
+        ops.TC_MIN_ROWS = 1 << 30 if flash else saved          # (the flash kernel serves where no portion is long enough for the other)
+        try:
+            plan = ops.plan_attention(q_lens, ctx_lens, page, (geo,), bf)
+        finally:
+            ops.TC_MIN_ROWS = saved
+        devplan = ModelRunner._device_plan(plan, {"plan_" + k: i32(v) for k, v in plan.items()}, (geo,))
+        actx = SimpleNamespace(cu_q=i32(cu), ctx_lens=i32(ctx_lens), q_lens_host=q_lens, ctx_lens_host=ctx_lens, attn_plan=devplan,
+                               arena=Arena(dev, 1 << 28))
+        timed(label, lambda: ops.paged_attention(qkv, pages, tables, actx, attn_out, D ** -0.5, 0, Hq, Hkv, D, **kw),
+              T * (Hq + 2 * Hkv + Hq) * D * 2, flops=2 * macs, like=None if not kw else label.split(",")[0] + "," + label.split(",")[1])
+        out[label]["kernel"] = ops.last_attention_kernel
+    ops.check_device_status()
+    return {"rows": T, "width": W, "kernels": out}
 
 
 def merudra_kernels_alone(torch, ops, peaks) -> dict:
@@ -601,7 +728,8 @@ def compare_designs(args) -> int:
     """``--compare ganidra``: prefill and decode of a Ganidra model beside a Qwen3 model of equal sizes (random weights,
     bfloat16), and the device time of every class of operation in one eager step of each (CUDA events around every
     call, the calls of a class added up).  ``--compare besavik``: a Besavik model beside both.  ``--compare merudra``: a
-    Merudra model beside a Besavik and a Qwen3 model.  Prints one JSON line."""
+    Merudra model beside a Besavik and a Qwen3 model.  ``--compare pufivik``: a Pufivik model beside a Merudra and a Qwen3
+    model.  Prints one JSON line."""
     import torch
     from qwen_engine_b200 import ops
     from qwen_engine_b200.config import preset_config_dict
@@ -709,21 +837,26 @@ def compare_designs(args) -> int:
         qraw = preset_config_dict(sz["preset"])
         qraw.update(num_hidden_layers=sz["layers"], vocab_size=sz["vocab"])
         out[name] = {"sizes": sz}
-        if args.compare == "merudra":
+        if args.compare == "pufivik":
+            out[name]["pufivik"] = measure(config_from_dict(pufivik_config_of(sz)), "pufivik")
+        if args.compare in ("merudra", "pufivik"):
             out[name]["merudra"] = measure(config_from_dict(merudra_config_of(sz)), "merudra")
         if args.compare in ("besavik", "merudra"):
             out[name]["besavik"] = measure(config_from_dict(besavik_config_of(sz)), "besavik")
-        if args.compare != "merudra":
+        if args.compare not in ("merudra", "pufivik"):
             out[name]["ganidra"] = measure(config_from_dict(ganidra_config_of(sz)), "ganidra")
         out[name]["qwen3"] = measure(config_from_dict(qraw), "qwen3")
-        designs = [d for d in ("merudra", "besavik", "ganidra", "qwen3") if d in out[name]]
+        designs = [d for d in ("pufivik", "merudra", "besavik", "ganidra", "qwen3") if d in out[name]]
         for other in designs[1:]:
             g, q = out[name][designs[0]], out[name][other]
             out[name][f"{designs[0]}_over_{other}"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
                                                       "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
-    alone = merudra_kernels_alone(torch, ops, peaks) if args.compare == "merudra" and not args.compare_size else None
+    alone = None
+    if not args.compare_size and args.compare in ("merudra", "pufivik"):
+        alone = (merudra_kernels_alone if args.compare == "merudra" else pufivik_kernels_alone)(torch, ops, peaks)
     clocks.stop()
-    title = {"besavik": "Besavik beside Ganidra and Qwen3", "merudra": "Merudra beside Besavik and Qwen3"}.get(args.compare, "Ganidra beside Qwen3")
+    title = {"besavik": "Besavik beside Ganidra and Qwen3", "merudra": "Merudra beside Besavik and Qwen3",
+             "pufivik": "Pufivik beside Merudra and Qwen3"}.get(args.compare, "Ganidra beside Qwen3")
     print(json.dumps({"metric": f"prefill and decode tok/s, {title} at equal sizes", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2",
                       "steps": args.steps, "warmup": args.warmup, "peaks": peaks_src, "sizes": out,
@@ -752,9 +885,9 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel-class timings")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--compare", choices=["ganidra", "besavik", "merudra"], default=None,
+    ap.add_argument("--compare", choices=["ganidra", "besavik", "merudra", "pufivik"], default=None,
                     help="instead of the default workload: prefill and decode of a Ganidra model beside a Qwen3 model of equal "
-                         "sizes (besavik: a Besavik model beside both; merudra: a Merudra model beside a Besavik and a Qwen3 model), with the device time of every class of operation "
+                         "sizes (besavik: a Besavik model beside both; merudra: a Merudra model beside a Besavik and a Qwen3 model; pufivik: a Pufivik model beside a Merudra and a Qwen3 model), with the device time of every class of operation "
                          "(one JSON line)")
     ap.add_argument("--compare-size", choices=sorted(COMPARE_SIZES), default=None, help="with --compare: one size only")
     args = ap.parse_args()

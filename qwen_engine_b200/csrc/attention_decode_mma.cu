@@ -105,7 +105,8 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
   const int* __restrict__ table = A.block_tables + (size_t)req * A.max_blocks;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   const size_t page_stride = (size_t)(A.kv_planes == 1 ? 1 : 2) * Hkv * page_size * D;
-  const size_t v_off = A.kv_planes == 1 ? 0 : (size_t)Hkv * page_size * D;
+  // (the values of kv head (hkv + v_shift) mod Hkv where the weights of this one are to meet another's)
+  const size_t v_off = A.kv_planes == 1 ? 0 : ((size_t)Hkv + (size_t)((hkv + A.v_shift) % Hkv) - (size_t)hkv) * page_size * D;
   const __nv_bfloat16* head_base = A.pages + (size_t)hkv * page_size * D;
   // a group that starts at a multiple of 16 keys lies in one page when pages are multiples of 16 keys
   const bool one_page = page_shift >= 4 && (kv_begin & 15) == 0;
@@ -202,6 +203,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
   const float slope_lo = biased ? A.slopes[hkv * G + g % G] * 1.4426950408889634f : 0.f;
   const float slope_hi = biased ? A.slopes[hkv * G + (g + 8) % G] * 1.4426950408889634f : 0.f;
   const int last_pos = first_pos + ntok - 1;
+  const float cap_in = A.softcap > 0.f ? A.scale / A.softcap : 0.f, cap_out = A.softcap * 1.4426950408889634f;   // bent scores
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[D / 8][4];
 #pragma unroll
@@ -220,7 +222,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
                           m_lo, m_hi, l_lo, l_hi, o, all_allowed, slope_lo, slope_hi);
     else
       fa_tile<D, 1>(sq, tk, tv, 0, 0, j0, kv_begin, kv_end, pos_lo, pos_hi, window, A.scale_log2, lane,
-                    m_lo, m_hi, l_lo, l_hi, o, all_allowed);
+                    m_lo, m_hi, l_lo, l_hi, o, all_allowed, 0.f, 0.f, cap_in, cap_out);
     __syncwarp();                                   // every lane is done with the stage before it is filled again
     const int nxt = gidx + DM_STAGES * DM_WARPS;
     if (nxt < n_groups) issue(nxt, st);
@@ -266,6 +268,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
       fin[r * D + d] = acc;
     } else if (part < 0) {
       const int ti = r / G, hg = r - ti * G;
+      if (A.sinks) l += exp2f(A.sinks[hkv * G + hg] * 1.4426950408889634f - mb);      // the sink's share of the denominator
       out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
       const size_t slot = ((size_t)part * Hkv + hkv) * A.part_rows + r;
@@ -335,6 +338,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
           }
         }
         const int ti = r / G, hg = r - ti * G;
+        if (A.sinks) l += exp2f(A.sinks[hkv * G + hg] * 1.4426950408889634f - mb);    // the sink's share of the denominator
         out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
       }
       return;
@@ -370,6 +374,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
           }
         }
         const int ti = r / G, hg = r - ti * G;
+        if (A.sinks) l += exp2f(A.sinks[hkv * G + hg] * 1.4426950408889634f - mb);    // the sink's share of the denominator
         out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
       }
     }
@@ -403,6 +408,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
           acc += wgt * __ldcg(A.part_acc + slot * D + d);
         }
         const int ti = r / G, hg = r - ti * G;
+        if (A.sinks) l += exp2f(A.sinks[hkv * G + hg] * 1.4426950408889634f - mb);    // the sink's share of the denominator
         out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
       }
     }
@@ -468,8 +474,10 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
                                        int max_blocks, const int* items, int n_items, void* out, float* part_acc,
                                        float* part_ml, int part_rows, int* counters, int max_rows, int cluster, int wide, float scale,
                                        int window, int Hq, int Hkv, int D, int page_size, const float* slopes, int kv_planes,
-                                       cudaStream_t stream) {
+                                       float softcap, const float* sinks, int v_shift, cudaStream_t stream) {
   if (n_items <= 0) return 0;
+  if (v_shift < 0 || v_shift >= Hkv || (v_shift && kv_planes == 1)) QE_REFUSE("decode_attention_mma: a shift of %d over %d kv heads", v_shift, Hkv);
+  if (slopes && softcap > 0.f) QE_REFUSE("decode_attention_mma: scores are biased by distance or bent, not both");
   if (!qe_decode_attention_mma_supported(Hq, Hkv, D, max_rows))
     QE_REFUSE("decode_attention_mma: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
   if ((((uintptr_t)q | (uintptr_t)pages | (uintptr_t)prefetch_pages) & 15) || (q_stride % 8))
@@ -478,7 +486,7 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention_mma: parts need the counters");
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
-            page_size, slopes, kv_planes};
+            page_size, slopes, kv_planes, softcap, scale, sinks, v_shift};
   if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);

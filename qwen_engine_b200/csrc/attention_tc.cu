@@ -77,6 +77,9 @@ struct AtArgs {
   float* part_acc; float* part_ml; int part_rows; int* counters;
   float scale_log2; int window, Hq, Hkv, page_shift;
   const float* slopes; float inv_scale;     // null, or float32 [Hq]: slopes[h] (position - key) is taken off the score
+  float cap_in, cap_mul;    // bent scores: the raw score s becomes cap_mul tanh(s cap_in), cap_in = scale / cap, cap_mul = cap / scale (0: as they are)
+  const float* sinks;       // null, or float32 [Hq]: exp(sinks[h]) joins head h's denominator (no key, no value)
+  int v_shift;              // the weights of a head of kv head c meet the values of kv head (c + v_shift) mod Hkv
 };
 
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
@@ -235,7 +238,8 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             int page = blk < A.max_blocks ? table[blk] : -1;
             if (page < 0) page = A.num_pages;       // outside the tensor: the box is filled with zeros
             __nv_bfloat16* dst = (kind ? sm.v[st][half] : sm.k[st][half]) + (size_t)box * box_rows * 64;
-            tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, U.hkv, kind, page);
+            tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y,
+                        kind ? (U.hkv + A.v_shift) % A.Hkv : U.hkv, kind, page);
           }
           if (kind) ++issued_v; else ++issued_k;
           if (kind == 0 && j == 0) {
@@ -453,6 +457,16 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
               for (int i = 0; i < 32; ++i)
                 s[c][i] = __float_as_uint(__uint_as_float(s[c][i]) + fmaf(kb, (float)(32 * c + i), b0));
           }
+          if (A.cap_in > 0.f) {
+            // bent scores: cap tanh(scale s / cap), kept in the raw scores' units so that the maxima, the scale and the
+            // exponentials below see them like any score; tanh z = 1 - 2 / (1 + e^(2 z)) with the hardware's exponential
+            const float ci = A.cap_in * 2.8853900817779268f, cm = A.cap_mul;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                s[c][i] = __float_as_uint(cm * (1.f - __fdividef(2.f, 1.f + at_ex2(__uint_as_float(s[c][i]) * ci))));
+          }
           float mx = -INFINITY;
           // A step's 128 keys as four runs of 32: where a run is allowed for all of the warp's rows (every run of a step
           // before the diagonal) the maxima are chains of three-input instructions; where it is forbidden for all of
@@ -582,7 +596,10 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       if (active && ok && role < 2) {
         {
           tc_fence_after();
-          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          // (a sink: exp(sinks[head]) joins the denominator of a whole row; a part's sum stays as it is for the merge)
+          const float l_all = (A.sinks && valid && part < 0 && l_run > 0.f)
+                                  ? l_run + exp2f(A.sinks[hkv * G + r % G] * 1.4426950408889634f - m_run) : l_run;
+          const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
           const size_t slot = part >= 0 ? ((size_t)part * Hkv + hkv) * A.part_rows + r : 0;
           const int wrow0 = w * AT_ROWS + quarter * 32;       // the warp's first row of the tile
           uint4* stage = sm.stage[warp];
@@ -667,6 +684,7 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             float l = 0.f;
 #pragma unroll
             for (int sp = 0; sp < P2; ++sp) { fw[k][sp] = exp2f(mm[sp] - mb); l += fw[k][sp] * ll[sp]; }
+            if (A.sinks && in && l > 0.f) l += exp2f(A.sinks[hkv * G + rr % G] * 1.4426950408889634f - mb);     // the sink's share
             const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
             for (int sp = 0; sp < P2; ++sp) fw[k][sp] *= inv;
@@ -907,7 +925,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
                                      const int* sched, int n_ctas,
                                      void* out, float* part_acc, float* part_ml, int part_rows, int* counters,
                                      float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                     const float* slopes, cudaStream_t stream) {
+                                     const float* slopes, float softcap, const float* sinks, int v_shift, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (sched == nullptr || n_ctas <= 0 || (long)n_ctas > (long)n_items * Hkv)
     QE_REFUSE("flash_attention_tc: a schedule for 1 to %ld CTAs is needed, not one for %d", (long)n_items * Hkv, n_ctas);
@@ -917,6 +935,8 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
   if ((((uintptr_t)q | (uintptr_t)pages | (uintptr_t)out) & 15) || (q_stride % 8))
     QE_REFUSE("flash_attention_tc: operands must be 16-byte aligned");
   if (scale <= 0.f) QE_REFUSE("flash_attention_tc: the scale must be positive");
+  if (v_shift < 0 || v_shift >= Hkv) QE_REFUSE("flash_attention_tc: a shift of %d over %d kv heads", v_shift, Hkv);
+  if (slopes && softcap > 0.f) QE_REFUSE("flash_attention_tc: scores are biased by distance or bent, not both");
   if ((long)n_items * Hkv > 0x7fffffffL) QE_REFUSE("flash_attention_tc: too many work items");
   const int G = Hq / Hkv;
   CUtensorMap map_q, map_kv;
@@ -936,7 +956,8 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   AtArgs args{block_tables, max_blocks, num_pages, items, sched, (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters,
-              scale * 1.4426950408889634f, window, Hq, Hkv, page_shift, slopes, 1.f / scale};
+              scale * 1.4426950408889634f, window, Hq, Hkv, page_shift, slopes, 1.f / scale,
+              softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sinks, v_shift};
   const size_t smem = sizeof(AtSmem) + 1024;
   static bool configured = false;
   if (!configured) {

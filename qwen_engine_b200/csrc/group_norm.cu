@@ -127,6 +127,74 @@ group_norm_kernel(const float* __restrict__ src, const TB* __restrict__ x, const
   }
 }
 
+// The same for rows whose parts are whole runs of 128 channels (a warp's 16-byte pieces of one turn lie in one part), up to
+// 1024 ITER channels: the row stays in registers, every load of a thread is on its way before the first sum, a warp's sum
+// of a turn is one partial sum, and a part's partial sums are added in their order.  Two meetings a norm.
+template <typename TB, typename TO, bool ADD, int ITER>
+__global__ void __launch_bounds__(GN_THREADS)
+group_norm_regs_kernel(const float* __restrict__ src, const TB* __restrict__ x, const int* __restrict__ rows,
+                       const float* __restrict__ w, float eps, int groups, int W, float* __restrict__ dst,
+                       const float* __restrict__ w_next, TO* __restrict__ out) {
+  __shared__ float part[ITER * (GN_THREADS / 32)];
+  __shared__ float inv[64];                              // (parts of at least 128 of at most 8192 channels)
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t at = (size_t)(rows ? rows[n] : n) * W;
+  const size_t to = (size_t)n * W;
+  const int gs = W / groups, per = gs >> 7;              // 128-channel runs in a part
+  float v[ITER][4];
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int d = (i * GN_THREADS + threadIdx.x) * 4;
+    if (d < W) gn_load4<TB>(x + at + d, v[i]);
+    else v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+  }
+  auto scales = [&]() {
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+      const float ss = warp_sum(fmaf(v[i][0], v[i][0], v[i][1] * v[i][1]) + fmaf(v[i][2], v[i][2], v[i][3] * v[i][3]));
+      if (lane == 0) part[i * (GN_THREADS / 32) + warp] = ss;
+    }
+    __syncthreads();
+    for (int g = threadIdx.x; g < groups; g += GN_THREADS) {
+      float ss = 0.f;
+      for (int p = 0; p < per; ++p) ss += part[g * per + p];
+      inv[g] = 1.f / sqrtf(ss / (float)gs + eps);
+    }
+    __syncthreads();
+  };
+  scales();
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int d = (i * GN_THREADS + threadIdx.x) * 4;
+    if (d >= W) continue;
+    const float sc = inv[d / gs];
+    const float4 wv = *reinterpret_cast<const float4*>(w + d);
+    float y[4] = {v[i][0] * sc * wv.x, v[i][1] * sc * wv.y, v[i][2] * sc * wv.z, v[i][3] * sc * wv.w};
+    if constexpr (ADD) {
+      const float4 sv = *reinterpret_cast<const float4*>(src + at + d);
+      v[i][0] = sv.x + y[0]; v[i][1] = sv.y + y[1]; v[i][2] = sv.z + y[2]; v[i][3] = sv.w + y[3];
+      *reinterpret_cast<float4*>(dst + at + d) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+    } else {
+      gn_store4<TO>(out + to + d, y);
+    }
+  }
+  if constexpr (ADD) {
+    if (out == nullptr) return;
+    scales();                                             // (every thread has read the first norm's scales: it met the others since)
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+      const int d = (i * GN_THREADS + threadIdx.x) * 4;
+      if (d >= W) continue;
+      const float sc = inv[d / gs];
+      const float4 wv = *reinterpret_cast<const float4*>(w_next + d);
+      float y[4] = {v[i][0] * sc * wv.x, v[i][1] * sc * wv.y, v[i][2] * sc * wv.z, v[i][3] * sc * wv.w};
+      gn_store4<TO>(out + to + d, y);
+    }
+  }
+}
+
 static int gn_check(const char* who, int W, int groups, size_t* smem) {
   if (groups < 1 || groups > GN_MAX_GROUPS || W < 1 || W % groups) QE_REFUSE("%s: %d channels do not split into %d equal parts", who, W, groups);
   *smem = ((size_t)((W + 3) & ~3) + (size_t)groups) * sizeof(float);
@@ -142,6 +210,11 @@ static int gn_configure(K kernel, size_t smem) {
   return 0;
 }
 
+#define GN_REGS(TB, TO, ADD, ...) do { \
+    if (W <= 1024) qe_launch(group_norm_regs_kernel<TB, TO, ADD, 1>, dim3(N), dim3(GN_THREADS), 0, stream, __VA_ARGS__); \
+    else if (W <= 2048) qe_launch(group_norm_regs_kernel<TB, TO, ADD, 2>, dim3(N), dim3(GN_THREADS), 0, stream, __VA_ARGS__); \
+    else if (W <= 4096) qe_launch(group_norm_regs_kernel<TB, TO, ADD, 4>, dim3(N), dim3(GN_THREADS), 0, stream, __VA_ARGS__); \
+    else qe_launch(group_norm_regs_kernel<TB, TO, ADD, 8>, dim3(N), dim3(GN_THREADS), 0, stream, __VA_ARGS__); } while (0)
 #define GN_LAUNCH(TB, TO, ADD, VEC, ...) do { auto kern_ = group_norm_kernel<TB, TO, ADD, VEC>; \
     if (int rc_ = gn_configure(kern_, smem)) return rc_; \
     qe_launch(kern_, dim3(N), dim3(GN_THREADS), smem, stream, __VA_ARGS__); } while (0)
@@ -152,9 +225,10 @@ extern "C" int qe_group_rmsnorm(const void* x, int x_dtype, const int* rows, con
   size_t smem = 0;
   if (int rc = gn_check("group_rmsnorm", W, groups, &smem)) return rc;
   const bool vec = W % 4 == 0 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
+  const bool regs = vec && W <= 8192 && (W / groups) % 128 == 0;
 #define GN_ARGS (const float*)nullptr, (const TB_*)x, rows, w, eps, groups, W, (float*)nullptr, (const float*)nullptr, (TO_*)out
-#define GN_PICK(TBT, TOT) do { using TB_ = TBT; using TO_ = TOT; if (vec) GN_LAUNCH(TBT, TOT, false, true, GN_ARGS); \
-    else GN_LAUNCH(TBT, TOT, false, false, GN_ARGS); } while (0)
+#define GN_PICK(TBT, TOT) do { using TB_ = TBT; using TO_ = TOT; if (regs) GN_REGS(TBT, TOT, false, GN_ARGS); \
+    else if (vec) GN_LAUNCH(TBT, TOT, false, true, GN_ARGS); else GN_LAUNCH(TBT, TOT, false, false, GN_ARGS); } while (0)
   if (x_dtype == QE_DTYPE_F32 && out_dtype == QE_DTYPE_F32) GN_PICK(float, float);
   else if (x_dtype == QE_DTYPE_F32 && out_dtype == QE_DTYPE_BF16) GN_PICK(float, __nv_bfloat16);
   else if (x_dtype == QE_DTYPE_BF16 && out_dtype == QE_DTYPE_BF16) GN_PICK(__nv_bfloat16, __nv_bfloat16);
@@ -175,9 +249,10 @@ extern "C" int qe_group_norm_add(const float* src, const void* branch, int branc
   if (next_out != nullptr && w_next == nullptr) QE_REFUSE("group_norm_add: the following norm needs its weights");
   if (next_out == nullptr) next_dtype = QE_DTYPE_F32;
   const bool vec = W % 4 == 0 && (((uintptr_t)src | (uintptr_t)branch | (uintptr_t)dst | (uintptr_t)next_out | (uintptr_t)w | (uintptr_t)w_next) & 15) == 0;
+  const bool regs = vec && W <= 8192 && (W / groups) % 128 == 0;
 #define GN_ARGS src, (const TB_*)branch, (const int*)nullptr, w, eps, groups, W, dst, w_next, (TO_*)next_out
-#define GN_PICK(TBT, TOT) do { using TB_ = TBT; using TO_ = TOT; if (vec) GN_LAUNCH(TBT, TOT, true, true, GN_ARGS); \
-    else GN_LAUNCH(TBT, TOT, true, false, GN_ARGS); } while (0)
+#define GN_PICK(TBT, TOT) do { using TB_ = TBT; using TO_ = TOT; if (regs) GN_REGS(TBT, TOT, true, GN_ARGS); \
+    else if (vec) GN_LAUNCH(TBT, TOT, true, true, GN_ARGS); else GN_LAUNCH(TBT, TOT, true, false, GN_ARGS); } while (0)
   if (branch_dtype == QE_DTYPE_F32 && next_dtype == QE_DTYPE_F32) GN_PICK(float, float);
   else if (branch_dtype == QE_DTYPE_F32 && next_dtype == QE_DTYPE_BF16) GN_PICK(float, __nv_bfloat16);
   else if (branch_dtype == QE_DTYPE_BF16 && next_dtype == QE_DTYPE_BF16) GN_PICK(__nv_bfloat16, __nv_bfloat16);

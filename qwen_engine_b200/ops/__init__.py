@@ -936,13 +936,6 @@ def geometry_planes(geo) -> int:
     return int(geo[5]) if len(geo) > 5 else 2
 
 
-def geometry_plain_kernels(geo) -> bool:
-    """The seventh entry of a geometry, if it has one: the mixer bends its scores, keeps a sink in the denominator or lets
-    a head's weights meet another kv head's values, which the flash and the generic kernel do and the kernels for head
-    size 128 alone do not."""
-    return bool(len(geo) > 6 and geo[6])
-
-
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                    geometries=(), dtype: torch.dtype = torch.float32,
                    uniform_splits: Optional[dict] = None) -> dict[str, list[int]]:
@@ -969,8 +962,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        use_tc = (uniform_splits is None and geometry_planes(geo) == 2 and not geometry_plain_kernels(geo)
-                  and tc_attention_supported(dtype, Hq, Hkv, D, page_size))
+        use_tc = uniform_splits is None and geometry_planes(geo) == 2 and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
         on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
         tc_tiles: list = []
         base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
@@ -1034,7 +1026,7 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
         span = min(max_tokens, window) if window else max_tokens
         target = FLASH_TARGET_CTAS
         if (DECODE_ATTENTION_MMA and DECODE_ATTENTION_MMA_WIDE and dtype == torch.bfloat16 and D == 128
-                and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS and not geometry_plain_kernels(geo)):
+                and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS):
             target = TC_TARGET_CTAS                                       # one CTA of 8 warps per SM
         want = max(1, target // max(1, num_reqs * Hkv))                   # all parts run in one wave
         parts = max(1, min(want, -(-span // FLASH_SPLIT)))
@@ -1099,7 +1091,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     ``softcap`` > 0: the scaled score s becomes softcap tanh(s / softcap).  ``sinks`` (float32 [Hq]): exp(sinks[h])
     joins the softmax's denominator of head h; it has no key and no value.  ``value_shift`` s: the weights of a head
     whose kv head is c meet the values of kv head (c + s) mod Hkv (a mixer that mixes the heads' weights sums such
-    outputs).  With any of the three, the mixer's geometry carries the mark of ``geometry_plain_kernels``.
+    outputs).  Every kernel takes the three (not together with a distance bias or a cache of one plane).
 
     ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
     pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
@@ -1121,15 +1113,11 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     if plain:
         _need(planes == 2 and slopes is None and 0 <= value_shift < Hkv,
               "paged_attention: bent scores, sinks and shifted values go with a cache of two planes and no distance bias")
-        key = index.get((Hq, Hkv, D, window, False, 2, True))
-        _need(key is None or f"tc{key}_items" not in plan, "paged_attention: the step's plan sends this mixer to a kernel that does not know its scores")
-    elif planes == 1:
+    if planes == 1:
         _need(slopes is None, "paged_attention: no distance bias over a cache of one plane")
         key = index.get((Hq, Hkv, D, window, False, 1))
     else:
         key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
-        if key is None and slopes is None:
-            key = index.get((Hq, Hkv, D, window, False, 2, True))      # (a mixer that is marked for the plain kernels and uses none of their options)
     if key is not None and f"tc{key}_items" in plan:
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
@@ -1145,7 +1133,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             int(block_tables.shape[1]), _ptr(tc_items), tc_items.numel() // FLASH_ITEM_INTS,
             _ptr(plan[f"tc{key}_sched"]), int(tc_ctas), _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(tc_rows), _ptr(counters), ctypes.c_float(scale), int(window),
-            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()), "flash_attention_tc")
+            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), ctypes.c_float(softcap), _ptr(sinks), int(value_shift), _stream()),
+            "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
         n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
@@ -1159,7 +1148,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
-        if not plain and _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
+        if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
             lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
@@ -1174,7 +1163,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
                 int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
-                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, _stream()),
+                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes,
+                ctypes.c_float(softcap), _ptr(sinks), int(value_shift), _stream()),
                 "decode_attention_mma")
             return
         last_attention_kernel = "flash_attention"

@@ -112,9 +112,7 @@ class GQAAttention(Mixer):
             raise ValueError(f"unknown value_mix {value_mix!r}")
         self.softcap = None if not softcap else float(softcap)
         self.sink, self.head_mixing, self.value_mix = bool(sink), bool(head_mixing), value_mix
-        # scores or values that only the flash and the generic kernel know
-        self.plain_kernels = bool(self.softcap or self.sink or self.head_mixing)
-        self.per_head = bool(self.plain_kernels or value_mix or output_gate == "sigmoid_head"
+        self.per_head = bool(self.softcap or self.sink or self.head_mixing or value_mix or output_gate == "sigmoid_head"
                              or getattr(self.pos, "row_permutation", None) is not None)
         if self.per_head and (self.tied_values or self.distance_slopes is not None or window or qk_norm_eps is not None):
             raise ValueError("bent scores, sinks, mixed heads, shared values and a gate per head go without a window, a distance "
@@ -141,8 +139,6 @@ class GQAAttention(Mixer):
 
     def attention_geometry(self):
         geo = (self.num_heads, self.num_kv_heads, self.head_dim, self.window or 0)
-        if self.plain_kernels:
-            return geo + (False, 2, True)
         return geo + (True,) if self.distance_slopes is not None else geo
 
     def weight_specs(self, prefix: str) -> list[WeightSpec]:

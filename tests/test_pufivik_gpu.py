@@ -220,7 +220,7 @@ def _attention_case(ops, dtype, H, G, D, P, q_lens, ctx_lens, softcap, sink, shi
             kv[sharp[1], 1] = 3.0
         for j in range(totals[r]):
             cache[tables[r, j // P], :, :, j % P] = kv[j].to(dtype)
-    geo = (H, G, D, 0, False, 2, True)
+    geo = (H, G, D, 0)
     plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, (geo,), dtype)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     devplan = ModelRunner._device_plan(plan, {"plan_" + k: i32(v) for k, v in plan.items()}, (geo,))
@@ -254,13 +254,26 @@ def test_attention_scores_bent_sunk_and_shifted(ops, dtype, H, G, D, P, softcap,
     out, want, kernel = _attention_case(ops, dtype, H, G, D, P, q_lens, ctx_lens, softcap, sink, shift, 11, sharp=(1, 3 * P))
     _close(out, want, dtype, f"{kernel}", tol={F32: 3e-5, BF16: 2e-2}[dtype])
     if dtype == BF16 and D % 16 == 0:
-        assert kernel == "flash_attention"
+        assert kernel != "paged_attention_generic"
     # the row of the sharpened key: unbent and without a sink it is that key's value; a cap or a sink takes its share
     row = want[70, :D]
     if softcap == 0.0 and not sink:
         assert float((row - 3.0).abs().max()) < 1e-3
     elif softcap > 0.0:
         assert float(row.abs().max()) < 2.0
+
+
+@pytest.mark.parametrize("softcap,sink,shift", [(0.0, False, 0), (4.0, False, 0), (0.0, True, 3), (2.5, True, 1)])
+def test_long_portions_at_head_size_128_on_the_tensor_memory_kernel(ops, softcap, sink, shift):
+    """Portions long enough for the tcgen05 kernel, whose tiles are cut into parts behind long contexts and merged (the
+    sink joins the merged denominator once), beside decoded tokens on the kernel for few rows; the same options."""
+    from helpers import LaunchSpy
+    H, G, D, P = 8, 4, 128, 16
+    with LaunchSpy() as spy:
+        out, want, kernel = _attention_case(ops, BF16, H, G, D, P, [300, 64, 1, 130, 1], [1000, 0, 3000, 77, 40], softcap, sink, shift, 21,
+                                            sharp=(0, 5 * P))
+    _close(out, want, BF16, kernel, tol=2e-2)
+    assert spy.count("qe_flash_attention_tc") == 1 and spy.count("qe_decode_attention_mma") + spy.count("qe_flash_attention_fused_merge") == 1
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
