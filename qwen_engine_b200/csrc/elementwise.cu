@@ -369,7 +369,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
                                              const float* __restrict__ inv_freq, int rotary_dim,
                                              T* __restrict__ pages, const int* __restrict__ slot_mapping,
                                              int T_tokens, int Hq, int Hkv, int D, int page_size, int write_kv, int norm_dim,
-                                             float magnitude, T* __restrict__ v_first, int v_mode, float v_lambda) {
+                                             float magnitude, T* __restrict__ v_first, int v_mode, float v_lambda, int v_dim) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -385,16 +385,18 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
   if (head >= Hq + Hkv) {           // a value head: copy into the cache
     const int h = head - Hq - Hkv;
     const T* src = v + (size_t)t * v_stride + (size_t)h * D;
-    // values shared across layers: v_mode 1 keeps this layer's values of the step's tokens in v_first [T, Hkv D];
-    // v_mode 2 caches (1 - v_lambda) v + v_lambda v_first instead of v (float32, rounded once)
-    T* first = v_mode ? v_first + ((size_t)t * Hkv + h) * D : nullptr;
-    if (v_mode == 1) for (int d = lane; d < D; d += 32) first[d] = src[d];
+    // values shared across layers: v_mode 1 keeps this layer's values of the step's tokens in v_first [T, Hkv, v_dim]
+    // (the head's own channels: layers may pad their heads differently); v_mode 2 caches (1 - v_lambda) v + v_lambda
+    // v_first instead of v (float32, rounded once; channels of padding stay zero)
+    T* first = v_mode ? v_first + ((size_t)t * Hkv + h) * v_dim : nullptr;
+    if (v_mode == 1) for (int d = lane; d < v_dim; d += 32) first[d] = src[d];
     if (!write_kv) return;
     const int slot = slot_mapping[t];
     const int page = slot / page_size, off = slot % page_size;
     T* dst = pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D;
     if (v_mode == 2)
-      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>((1.f - v_lambda) * to_f32(src[d]) + v_lambda * to_f32(first[d]));
+      for (int d = lane; d < D; d += 32)
+        dst[d] = from_f32<T>((1.f - v_lambda) * to_f32(src[d]) + (d < v_dim ? v_lambda * to_f32(first[d]) : 0.f));
     else
       for (int d = lane; d < D; d += 32) dst[d] = src[d];
     return;
@@ -498,10 +500,11 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
                                         const float* inv_freq, const void* cos_sin, int rotary_dim, void* pages,
                                         const int* slot_mapping, int T, int Hq, int Hkv, int D, int page_size,
                                         int write_kv, int dtype, int norm_dim, float magnitude, void* v_first, int v_mode,
-                                        float v_lambda, cudaStream_t stream) {
+                                        float v_lambda, int v_dim, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (norm_dim <= 0) norm_dim = D;
-  if (v_mode < 0 || v_mode > 2 || (v_mode && !v_first)) QE_REFUSE("qk_norm_rope_kv_write: values shared across layers need their buffer");
+  if (v_mode < 0 || v_mode > 2 || (v_mode && (!v_first || v_dim < 1 || v_dim > D)))
+    QE_REFUSE("qk_norm_rope_kv_write: values shared across layers need their buffer, of 1 to %d channels a head", D);
   if (D > QKR_MAX_D) QE_REFUSE("qk_norm_rope_kv_write: head_dim %d is above %d", D, QKR_MAX_D);
   if (inv_freq && (rotary_dim % 2 || rotary_dim > D || rotary_dim <= 0))
     QE_REFUSE("qk_norm_rope_kv_write: rotary_dim %d does not fit head_dim %d", rotary_dim, D);
@@ -531,12 +534,12 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
     qe_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
         (float*)q, (float*)k, (const float*)v, q_stride, k_stride, v_stride, positions, qw, kw, eps, inv_freq,
         rotary_dim, (float*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv, norm_dim, magnitude, (float*)v_first,
-        v_mode, v_lambda);
+        v_mode, v_lambda, v_dim);
   else if (dtype == QE_DTYPE_BF16)
     qe_launch(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
         (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions, qw, kw,
         eps, inv_freq, rotary_dim, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv, norm_dim, magnitude,
-        (__nv_bfloat16*)v_first, v_mode, v_lambda);
+        (__nv_bfloat16*)v_first, v_mode, v_lambda, v_dim);
   else QE_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
   return 0;

@@ -811,7 +811,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     ``kv_pages`` [pages, 2, Hkv, page, D].  ``norm_dim``: the channels the norm's mean runs over, where a
     head is padded with zero channels up to D.  ``magnitude``: cosines and sines are multiplied by it.
     ``value_mix``: values shared across layers, ("keep", first) copies this layer's values of the step's tokens into
-    ``first`` [T, Hkv D]; ("blend", first, lam) caches (1 - lam) v + lam first in the place of v."""
+    ``first`` [T, Hkv Dv] (Dv <= D: the heads' own channels, without padding); ("blend", first, lam) caches
+    (1 - lam) v + lam first in the place of v."""
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     _need(qkv.shape == (T, (Hq + 2 * Hkv) * D) and qkv.stride(1) == 1, "qk_norm_rope_kv_write: qkv must be [T, (Hq+2Hkv)D]")
@@ -835,13 +836,15 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
               "qk_norm_rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
-    v_first, v_mode, v_lambda = None, 0, 0.0
+    v_first, v_mode, v_lambda, v_dim = None, 0, 0.0, D
     if value_mix is not None:
         _need(value_mix[0] in ("keep", "blend"), "qk_norm_rope_kv_write: value_mix is ('keep', first) or ('blend', first, lam)")
         v_first, v_mode = value_mix[1], 1 if value_mix[0] == "keep" else 2
         v_lambda = float(value_mix[2]) if v_mode == 2 else 0.0
-        _need(v_first.shape == (T, Hkv * D) and v_first.dtype == qkv.dtype and v_first.is_contiguous(),
-              "qk_norm_rope_kv_write: the shared values must be contiguous [T, Hkv D] in qkv's dtype")
+        _need(v_first.dim() == 2 and v_first.shape[0] == T and v_first.shape[1] % Hkv == 0 and 1 <= v_first.shape[1] // Hkv <= D
+              and v_first.dtype == qkv.dtype and v_first.is_contiguous(),
+              "qk_norm_rope_kv_write: the shared values must be contiguous [T, Hkv Dv] in qkv's dtype, Dv <= D")
+        v_dim = v_first.shape[1] // Hkv
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
@@ -849,7 +852,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
         _ptr(cos_sin if (cos_sin is not None and D == 128 and rotary_dim == D) else None), int(rotary_dim),
         _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
         T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), int(norm_dim or D), ctypes.c_float(magnitude), _ptr(v_first),
-        v_mode, ctypes.c_float(v_lambda), _stream()), "qk_norm_rope_kv_write")
+        v_mode, ctypes.c_float(v_lambda), int(v_dim), _stream()), "qk_norm_rope_kv_write")
 
 
 def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
@@ -864,7 +867,7 @@ def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fre
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(0),
         ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(0), _ptr(positions),
         _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), _ptr(None), int(rotary_dim),
-        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), D, ctypes.c_float(1.0), _ptr(None), 0, ctypes.c_float(0.0),
+        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), D, ctypes.c_float(1.0), _ptr(None), 0, ctypes.c_float(0.0), D,
         _stream()), "rope_neox")
 
 

@@ -279,11 +279,11 @@ class GQAAttention(Mixer):
         if self.value_mix:
             first = step_hint(ctx, "shared_values")
             if self.value_mix == "keep":
-                first = ctx.arena.alloc_step((T, self.kv_width), ctx.dtype)
+                first = ctx.arena.alloc_step((T, Hkv * self.value_dim), ctx.dtype)     # (the heads' own channels: layers pad differently)
                 ctx.extras["shared_values"] = first
                 shared = ("keep", first)
             else:
-                if first is None or first.shape != (T, self.kv_width):
+                if first is None or first.shape != (T, Hkv * self.value_dim):
                     raise RuntimeError("gqa_attention: values to blend with, but no layer before this one kept its own")
                 shared = ("blend", first, self.mix_lambda)
         rot = self.pos.half_split_rotation() if self.pos is not None else None

@@ -41,11 +41,12 @@ def _model(vocab, width, eps, groups, taps, scale, mult, layers):
 
 
 PUFIVIK = {
-    # grouped kv heads; bent scores first (it keeps its values), the sink mixer blends; a last layer without
-    # feed-forward that shares no values; half a head rotated in one mixer, the whole head in the other
+    # grouped kv heads; bent scores first (it keeps its values), the sink mixer blends (its heads are padded to another
+    # size than the keeping layer's); a last layer without feed-forward that shares no values; half a head rotated in one
+    # mixer, two thirds in the other
     "p-a": dict(cfg=_model(211, 64, 1e-6, 2, 2, 3.0, 0.7, [
         _with(_capped(4, 2, 16, 8, 0.25, 5.0, _ramp(10000.0, 8, 8.0, 64, 16.0, 2.0), True), _moe(5, 2, 24)),
-        _with(_sink(4, 2, 16, 8, 0.3, _bands(5000.0, 16, 8.0, 1.0, 4.0, 32), True), _moe(3, 1, 16)),
+        _with(_sink(4, 2, 24, 8, 0.3, _bands(5000.0, 16, 8.0, 1.0, 4.0, 32), True), _moe(3, 1, 16)),
         _with(_capped(2, 1, 32, 16, 0.2, 2.0, _ramp(300.0, 32, 2.0, 16, 4.0, 1.0), False), None)]), seed=3, std=0.12, norm_std=0.2, page=4),
     # no grouping (three heads over three kv heads); values wider than keys; the sink mixer first keeps the values; all
     # experts chosen; one norm group; no frequency scaling in one layer; four taps

@@ -103,11 +103,14 @@ def qk_norm_rope_kv_write(qkv, positions, q_norm_w, k_norm_w, eps, inv_freq, rot
         q = _rotate(q, positions, inv_freq, rotary_dim, magnitude)
         k = _rotate(k, positions, inv_freq, rotary_dim, magnitude)
     if value_mix is not None:
+        dv = value_mix[1].shape[1] // Hkv                  # the heads' own channels (layers pad differently)
         if value_mix[0] == "keep":
-            value_mix[1].copy_(v.reshape(T, Hkv * D))
+            value_mix[1].copy_(v[:, :, :dv].reshape(T, Hkv * dv))
         else:
             lam = float(value_mix[2])
-            v = ((1.0 - lam) * v.to(torch.float32) + lam * value_mix[1].reshape(T, Hkv, D).to(torch.float32)).to(qkv.dtype)
+            first = torch.zeros(T, Hkv, D, dtype=torch.float32)
+            first[:, :, :dv] = value_mix[1].reshape(T, Hkv, dv).to(torch.float32)
+            v = ((1.0 - lam) * v.to(torch.float32) + lam * first).to(qkv.dtype)
     qkv[:, :Hq * D] = q.reshape(T, Hq * D).to(qkv.dtype)
     qkv[:, Hq * D:(Hq + Hkv) * D] = k.reshape(T, Hkv * D).to(qkv.dtype)
     if write_kv:

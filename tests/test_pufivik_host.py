@@ -61,7 +61,7 @@ def test_caches_of_the_layers():
     assert [type(s).__name__ for s in specs] == ["PagedKVSpec", "FixedStateSpec"] * 3
     assert (specs[0].num_kv_heads, specs[0].head_dim, specs[0].planes) == (2, 16, 2) and specs[1].shape == (1, 64)
     assert (specs[4].num_kv_heads, specs[4].head_dim) == (1, 32)
-    assert model.attention_geometries == ((4, 2, 16, 0), (2, 1, 32, 0))
+    assert model.attention_geometries == ((4, 2, 16, 0), (4, 2, 24, 0), (2, 1, 32, 0)) and specs[2].head_dim == 24
     model = build_model(config_from_dict(ph.PUFIVIK["p-b"]["cfg"]))
     assert model.cache_specs()[0].head_dim == 32 and model.cache_specs()[1].shape == (3, 96)
     model = build_model(config_from_dict(ph.PUFIVIK["p-c"]["cfg"]))
