@@ -81,6 +81,25 @@ PRESETS: dict[str, dict[str, Any]] = {
                                  mixer=dict(heads=4, kv_heads=2, dim=32, vdim=32, scale=0.18, q_temp=dict(coef=0.3, every=16)),
                                  mlp=None)]),
         init=dict(seed=11, std=0.08, norm_std=0.1, block_size=16)),
+    # a small model of the Pufivik design: norms in two groups around every sublayer, the mixers' input through
+    # convolutions of 3 taps, attention with bent scores and attention with a sink, mixed heads and a gate per head, keys
+    # of 32 and values of 16 channels, values blended with the first layer's, experts scored by sigmoids
+    "pufivik-tiny": dict(
+        config=dict(architecture="Pufivik", vocab=320, width=128, norm=dict(eps=1e-6, groups=2), canon=dict(taps=3),
+                    embedding=dict(scale=4.0), residual_mult=0.6,
+                    layers=[dict(type="attention_2",
+                                 mixer=dict(heads=4, kv_heads=2, dim=32, vdim=16, scale=0.18, softcap=20.0, v_mix=True,
+                                            rot=dict(base=10000.0, dims=16, scaling=dict(factor=4.0, original=64, fast=16.0, slow=1.0))),
+                                 mlp=dict(kind="moe", expert=dict(ff=64), router=dict(experts=4, top=2))),
+                            dict(type="attention",
+                                 mixer=dict(heads=4, kv_heads=2, dim=32, vdim=16, scale=0.18, v_mix=True,
+                                            rot=dict(base=50000.0, dims=32, scaling=dict(factor=8.0, low=1.0, high=4.0, original=128))),
+                                 mlp=dict(kind="moe", expert=dict(ff=64), router=dict(experts=4, top=1))),
+                            dict(type="attention_2",
+                                 mixer=dict(heads=2, kv_heads=2, dim=16, vdim=16, scale=0.25, softcap=8.0, v_mix=True,
+                                            rot=dict(base=10000.0, dims=8, scaling=None)),
+                                 mlp=None)]),
+        init=dict(seed=17, std=0.08, norm_std=0.1, block_size=16)),
 }
 
 
