@@ -55,8 +55,10 @@ def _check_mixer(where: str, kind: str, m: Any) -> None:
             _number(f"{where}.rot.scaling.{key}", scaling.get(key))
         if kind == "attention" and scaling["high"] == scaling["low"]:
             raise ConfigError(f"config.json: {where}.rot.scaling.high and .low must differ")
-    if kind == "attention_2":
-        _number(f"{where}.softcap", m.get("softcap"))
+    if m.get("softcap") is not None:                # (absent or null: the scores stay as they are)
+        if kind != "attention_2":
+            raise ConfigError(f"config.json: {where}.softcap belongs to the mixer 'attention_2'")
+        _number(f"{where}.softcap", m["softcap"])
 
 
 def _check_mlp(where: str, mlp: Any) -> None:

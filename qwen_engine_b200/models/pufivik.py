@@ -38,7 +38,7 @@ def _mixer(cfg: PufivikConfig, layer: dict, value_mix) -> PartSpec:
                   scale=m["scale"], position_encoding=_position_encoding(kind, m), value_mix=value_mix, names=names)
     if kind == "attention":
         return PartSpec("gqa_attention", dict(common, sink=True, head_mixing=True, output_gate="sigmoid_head"))
-    return PartSpec("gqa_attention", dict(common, softcap=m["softcap"]))
+    return PartSpec("gqa_attention", dict(common, softcap=m.get("softcap")))
 
 
 def _feed_forward(cfg: PufivikConfig, mlp):

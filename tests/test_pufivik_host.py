@@ -35,7 +35,8 @@ def test_config_reads_its_own_keys_and_round_trips():
 @pytest.mark.parametrize("change, text", [
     (lambda c: c["layers"][0].update(type="delta"), "not a mixer"),
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "multiple of kv_heads"),
-    (lambda c: c["layers"][0]["mixer"].pop("softcap"), "softcap"),
+    (lambda c: c["layers"][0]["mixer"].update(softcap=0.0), "softcap"),
+    (lambda c: c["layers"][1]["mixer"].update(softcap=3.0), "belongs to"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=18), "at most dim"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "even"),
     (lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].pop("high"), "scaling.high"),
