@@ -94,7 +94,7 @@ def test_a_sublayers_way_back_with_the_next_norm_in_the_same_pass(ops, dtype, T,
 
 # ---- heads mixed and gated ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H,G,D", [(1, 4, 2, 16), (9, 3, 3, 24), (70, 8, 4, 128), (33, 6, 1, 20), (5, 2, 2, 96)])
+@pytest.mark.parametrize("T,H,G,D", [(1, 4, 2, 16), (9, 3, 3, 24), (70, 8, 4, 128), (33, 6, 1, 20), (5, 2, 2, 80)])
 def test_heads_mixed_and_gated(ops, dtype, T, H, G, D):
     g = torch.Generator().manual_seed(T + H + D)
     partial = torch.randn(G, T, H * D, generator=g).to(dtype)
@@ -157,7 +157,7 @@ def test_experts_that_read_their_weighted_input(ops, dtype, T, W, I, E, top):
 
 # ---- rotation with a magnitude, values shared across layers, the cache write -------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,R,P", [(4, 2, 16, 8, 4), (3, 3, 24, 24, 8), (2, 1, 96, 48, 16), (4, 2, 128, 128, 16), (1, 1, 20, 6, 8)])
+@pytest.mark.parametrize("H,G,D,R,P", [(4, 2, 16, 8, 4), (3, 3, 24, 24, 8), (2, 1, 80, 40, 16), (4, 2, 128, 128, 16), (1, 1, 20, 6, 8)])
 def test_rotation_magnitude_and_blended_values_into_the_cache(ops, dtype, H, G, D, R, P):
     T, pages = 37, 16           # (pages x P slots: more than tokens for every P)
     g = torch.Generator().manual_seed(D + R)
@@ -166,7 +166,7 @@ def test_rotation_magnitude_and_blended_values_into_the_cache(ops, dtype, H, G, 
     inv = torch.rand(R // 2, generator=g)
     slots = torch.randperm(pages * P, generator=g)[:T].to(torch.int32)
     mag, lam = 1.27, 0.35
-    dv = D // 2 if P == 4 or D == 96 else D               # kept values may have fewer channels than the padded head
+    dv = D // 2 if P == 4 or D == 80 else D               # kept values may have fewer channels than the padded head
     first = torch.randn(T, G * dv, generator=g).to(dtype)
     for mode in ("keep", "blend", None):
         cache = torch.full((pages, 2, G, P, D), 7.0, dtype=dtype, device=DEV)
@@ -248,7 +248,7 @@ def _attention_case(ops, dtype, H, G, D, P, q_lens, ctx_lens, softcap, sink, shi
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,P", [(4, 2, 96, 16), (8, 4, 128, 16), (3, 3, 32, 8), (6, 1, 64, 4), (2, 2, 20, 8)])
+@pytest.mark.parametrize("H,G,D,P", [(4, 2, 80, 16), (8, 4, 128, 16), (3, 3, 32, 8), (6, 1, 64, 4), (2, 2, 20, 8)])
 @pytest.mark.parametrize("softcap,sink,shift", [(0.0, False, 0), (1.5, False, 0), (0.0, True, 0), (0.0, True, 1), (2.0, True, 0)])
 def test_attention_scores_bent_sunk_and_shifted(ops, dtype, H, G, D, P, softcap, sink, shift):
     """Prompt portions behind contexts beside decoded tokens (one far back in a long context, which the kernels cut into
@@ -285,7 +285,7 @@ def test_long_portions_at_head_size_128_on_the_tensor_memory_kernel(ops, softcap
 def test_single_decoded_tokens_alone_and_from_the_first_token(ops, dtype):
     """Steps of single tokens only (the kernels' layout for few rows, contexts in parts that are merged with the sink):
     contexts of 0, 1, a page less one, a page, and thousands of keys."""
-    for H, G, D, P in ((4, 2, 96, 16), (8, 2, 128, 16), (2, 1, 48, 8)):
+    for H, G, D, P in ((4, 2, 80, 16), (8, 2, 128, 16), (2, 1, 48, 8)):
         ctx_lens = [0, 1, P - 1, P, 2500, 700]
         out, want, kernel = _attention_case(ops, dtype, H, G, D, P, [1] * 6, ctx_lens, 3.0, True, 0, 5, sharp=(4, P))
         _close(out, want, dtype, kernel, tol={F32: 3e-5, BF16: 2e-2}[dtype])
@@ -360,8 +360,8 @@ def _mixer_and_weights(kind, m, W, dtype, seed, value_mix):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("kind,H,G,D,Dv,R,P", [("attention", 4, 2, 96, 32, 48, 16), ("attention", 8, 4, 128, 128, 64, 16), ("attention", 3, 3, 16, 40, 16, 8),
-                                               ("attention_2", 4, 2, 96, 32, 48, 16), ("attention_2", 4, 1, 128, 64, 128, 16), ("attention_2", 2, 2, 24, 8, 6, 4)])
+@pytest.mark.parametrize("kind,H,G,D,Dv,R,P", [("attention", 4, 2, 80, 48, 40, 16), ("attention", 8, 4, 128, 128, 64, 16), ("attention", 3, 3, 16, 40, 16, 8),
+                                               ("attention_2", 4, 2, 80, 48, 40, 16), ("attention_2", 4, 1, 128, 64, 128, 16), ("attention_2", 2, 2, 24, 8, 6, 4)])
 @pytest.mark.parametrize("decoded", [False, True])
 def test_a_mixer_through_its_cache_with_a_far_key_that_stands_out(ops, dtype, kind, H, G, D, Dv, R, P, decoded):
     """Every row of 700 tokens against the plain mixer, cut into a long portion and a short one or into a prompt and
