@@ -50,7 +50,8 @@ __device__ __forceinline__ void dm_cp_async16_zfill(void* smem, const void* gmem
 
 template <bool CL, int DM_STAGES, int DM_WARPS>
 __global__ void __launch_bounds__(DM_WARPS * 32, DM_WARPS == 4 ? 2 : 1)
-decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue, int push_rows) {
+decode_attention_mma_kernel(FaArgs A_launch, long long prefetch_delta, int early_issue, int push_rows) {
+  const FaArgs A = fa_for_shift(A_launch, blockIdx.z, DM_D);       // (several shifts of the values' kv head in one launch)
   constexpr int DM_THREADS = DM_WARPS * 32;
   constexpr int DM_WARP_BYTES = DM_WARP_BYTES_OF(DM_STAGES);
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -429,7 +430,7 @@ static int g_dm_push = 1;
 extern "C" void qe_decode_attention_mma_push(int on) { g_dm_push = on ? 1 : 0; }
 
 template <bool CL, int STAGES, int WARPS>
-static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int max_rows, cudaStream_t stream) {
+static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int max_rows, cudaStream_t stream, int shifts) {
   constexpr int base_smem = DM_SMEM_BYTES_OF(STAGES, WARPS);
   constexpr int limit = 226 * 1024;                 // (an SM has 227 KB; the kernel's static variables take some)
   // the in-boxes of the other parts behind the warps' memory, if they fit
@@ -443,18 +444,19 @@ static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int 
     configured = CL ? limit : base_smem;
   }
   if (CL)
-    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta, g_dm_early, push_rows);
+    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv, shifts), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta, g_dm_early, push_rows);
   else
-    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta, g_dm_early, 0);
+    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv, shifts), dim3(WARPS * 32), smem, stream, fa, prefetch_delta, g_dm_early, 0);
   QE_CHECK_LAUNCH("decode_attention_mma");
   return 0;
 }
 // wide: CTAs of 8 warps, one per SM (for steps whose items are at most as many as SMs), else 4 warps, two per SM
 template <bool CL>
-static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int wide, int max_rows, cudaStream_t stream) {
-  if (wide) return launch_decode_mma_as<CL, 3, 8>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream);
-  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream)
-                          : launch_decode_mma_as<CL, 2, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream);
+static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int wide, int max_rows, cudaStream_t stream,
+                             int shifts) {
+  if (wide) return launch_decode_mma_as<CL, 3, 8>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream, shifts);
+  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream, shifts)
+                          : launch_decode_mma_as<CL, 2, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream, shifts);
 }
 
 // Whether the kernel takes this geometry with at most max_rows rows (token x head of the group) per item:
@@ -474,8 +476,10 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
                                        int max_blocks, const int* items, int n_items, void* out, float* part_acc,
                                        float* part_ml, int part_rows, int* counters, int max_rows, int cluster, int wide, float scale,
                                        int window, int Hq, int Hkv, int D, int page_size, const float* slopes, int kv_planes,
-                                       float softcap, const float* sinks, int v_shift, cudaStream_t stream) {
+                                       float softcap, const float* sinks, int v_shift, int shifts, long shift_out_stride,
+                                       int shift_parts, cudaStream_t stream) {
   if (n_items <= 0) return 0;
+  if (shifts < 1 || shifts > Hkv || (shifts > 1 && kv_planes == 1)) QE_REFUSE("decode_attention_mma: %d shifts in one launch over %d kv heads", shifts, Hkv);
   if (v_shift < 0 || v_shift >= Hkv || (v_shift && kv_planes == 1)) QE_REFUSE("decode_attention_mma: a shift of %d over %d kv heads", v_shift, Hkv);
   if (slopes && softcap > 0.f) QE_REFUSE("decode_attention_mma: scores are biased by distance or bent, not both");
   if (!qe_decode_attention_mma_supported(Hq, Hkv, D, max_rows))
@@ -486,11 +490,11 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention_mma: parts need the counters");
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
-            page_size, slopes, kv_planes, softcap, scale, sinks, v_shift};
-  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream);
+            page_size, slopes, kv_planes, softcap, scale, sinks, v_shift, shift_out_stride, shift_parts};
+  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream, shifts);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);
-  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, wide, max_rows, stream);
+  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, wide, max_rows, stream, shifts);
 }
 
 // The status word of the bounded wait for the pushed parts (0 = fine).

@@ -6,7 +6,8 @@ template <int D, int STAGES, int QROWS>
 __global__ void __launch_bounds__(2 * FA_THREADS, (D <= 128 ? 2 : 1))
 flash_attention_kernel(FaArgs args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  flash_attention_cta<D, STAGES, QROWS, false>(args, blockIdx.x, blockIdx.y, smem_raw);
+  const FaArgs mine = fa_for_shift(args, blockIdx.z, D);
+  flash_attention_cta<D, STAGES, QROWS, false>(mine, blockIdx.x, blockIdx.y, smem_raw);
 }
 
 // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s  (reference attn.py:520-594), float32.
@@ -53,7 +54,7 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
                         const int* merge_items, int n_merge, void* out, float* part_acc, float* part_ml,
                         int part_rows, int* counters, float scale, int window, int Hq, int Hkv, int page_size,
                         const float* slopes, int kv_planes, float softcap, const float* sinks, int v_shift,
-                        cudaStream_t stream) {
+                        int shifts, long shift_out_stride, int shift_parts, cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(QROWS + 2 * STAGES * FA_BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
@@ -63,10 +64,10 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(n_items, Hkv);
+  dim3 grid(n_items, Hkv, shifts);
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale_log2, window, Hq, Hkv, page_size, slopes, kv_planes,
-            softcap, scale, sinks, v_shift};
+            softcap, scale, sinks, v_shift, shift_out_stride, shift_parts};
   qe_launch(flash_attention_kernel<D, STAGES, QROWS>, grid, dim3(2 * FA_THREADS), smem, stream, fa);
   QE_CHECK_LAUNCH("flash_attention");
   if (n_merge > 0 && counters == nullptr) {
@@ -102,7 +103,8 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
                                               int small_tiles, float scale, int window, int Hq, int Hkv, int D,
                                               int page_size, const float* slopes, int kv_planes, float softcap,
-                                              const float* sinks, int v_shift, cudaStream_t stream);
+                                              const float* sinks, int v_shift, int shifts, long shift_out_stride,
+                                              int shift_parts, cudaStream_t stream);
 
 extern "C" int qe_flash_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
                                   int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
@@ -111,7 +113,7 @@ extern "C" int qe_flash_attention(const void* q, long q_stride, const void* page
                                   int page_size, cudaStream_t stream) {
   return qe_flash_attention_fused_merge(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items,
                                         merge_items, n_merge, out, part_acc, part_ml, part_rows, nullptr, 0, scale,
-                                        window, Hq, Hkv, D, page_size, nullptr, 2, 0.f, nullptr, 0, stream);
+                                        window, Hq, Hkv, D, page_size, nullptr, 2, 0.f, nullptr, 0, 1, 0, 0, stream);
 }
 
 extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, const void* pages, const int* block_tables,
@@ -120,7 +122,8 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
                                               int small_tiles, float scale, int window, int Hq, int Hkv, int D,
                                               int page_size, const float* slopes, int kv_planes, float softcap,
-                                              const float* sinks, int v_shift, cudaStream_t stream) {
+                                              const float* sinks, int v_shift, int shifts, long shift_out_stride,
+                                              int shift_parts, cudaStream_t stream) {
   // small_tiles: every item has at most 16 rows (a decode step): 16 query rows are staged and the key
   // tiles run through a deeper pipeline
   if (n_items <= 0) return 0;
@@ -128,9 +131,13 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
     QE_REFUSE("flash_attention: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
   if (((uintptr_t)q | (uintptr_t)pages) & 15 || (q_stride % 8)) QE_REFUSE("flash_attention: operands must be 16-byte aligned");
   if (v_shift < 0 || v_shift >= Hkv || (v_shift && kv_planes == 1)) QE_REFUSE("flash_attention: a shift of %d over %d kv heads", v_shift, Hkv);
+  // several shifts in one launch: each has its own output, parts and counters; the merge kernel is not laid out for them
+  if (shifts < 1 || shifts > Hkv || (shifts > 1 && (kv_planes == 1 || (n_merge > 0 && counters == nullptr))))
+    QE_REFUSE("flash_attention: %d shifts in one launch over %d kv heads", shifts, Hkv);
   if (slopes && softcap > 0.f) QE_REFUSE("flash_attention: scores are biased by distance or bent, not both");
 #define FA_ARGS q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items, merge_items, n_merge, out, \
-      part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, slopes, kv_planes, softcap, sinks, v_shift, stream
+      part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, slopes, kv_planes, softcap, sinks, v_shift, \
+      shifts, shift_out_stride, shift_parts, stream
 #define FA_CASE(DD) case DD: return small_tiles ? launch_flash<DD, 3, 16>(FA_ARGS) : launch_flash<DD, 2, FA_BM>(FA_ARGS);
   switch (D) {
     FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)

@@ -278,7 +278,24 @@ struct FaArgs {
   float scale;              // the scale itself (scale_log2 / log2 e), for the bent scores
   const float* sinks;       // null, or float32 [Hq]: exp(sinks[h]) joins head h's denominator (no key, no value)
   int v_shift;              // the weights of a head of kv head c meet the values of kv head (c + v_shift) mod Hkv
+  // Several shifts in one launch (grid dimension z): CTAs of z work with v_shift + z and with their own share of the
+  // output, of the parts' scratch and of the counters (fa_for_shift moves the pointers, so nothing else sees it).
+  long shift_out_stride;    // elements between the outputs of two shifts
+  int shift_parts;          // parts of one shift (their scratch and counters are laid out shift after shift)
 };
+
+__device__ __forceinline__ FaArgs fa_for_shift(const FaArgs& in, int z, int head_dim) {
+  FaArgs A = in;
+  if (z > 0) {
+    A.v_shift = (in.v_shift + z) % in.Hkv;
+    A.out = in.out + (size_t)z * in.shift_out_stride;
+    const size_t slots = (size_t)z * in.shift_parts * in.Hkv * in.part_rows;
+    if (in.part_acc) A.part_acc = in.part_acc + slots * head_dim;
+    if (in.part_ml) A.part_ml = in.part_ml + 2 * slots;
+    if (in.counters) A.counters = in.counters + (size_t)z * in.shift_parts * in.Hkv;
+  }
+  return A;
+}
 
 // The work of one CTA (work item `item_idx`, kv head `hkv`) by 256 threads; `smem_raw`: the dynamic
 // shared memory (16-byte aligned).  PERSIST: the caller is a kernel that goes on after this call

@@ -49,6 +49,7 @@ DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
 DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
 DECODE_ATTENTION_MMA_EARLY = True   # that kernel requests earlier steps' keys before it waits for the kernel before it
 DECODE_ATTENTION_MMA_BESIDE_TC = True   # also for the decoded tokens of a step whose prompt portions go to the tcgen05 kernel
+SHIFTS_IN_ONE_LAUNCH = True          # a mixer that mixes its heads' weights: the shifts of the values' kv head as one launch where the step has no long portion
 DECODE_ATTENTION_MMA_WIDE = True    # steps with at most as many attention CTAs as SMs: CTAs of 8 warps, one per SM (and contexts split for 148 CTAs, not 296)
 DECODE_PREFETCH_KV_MB = 12          # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never).  Measured (0.6B, context 1 024, asked for before the kernel's dependency wait): 4.4 MB (one request) 0.698 -> 0.690 ms a step, 8.8 MB 0.777 -> 0.765, 17.6 MB equal, 35 MB (eight) 0.915 -> 0.957
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
@@ -1084,7 +1085,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
                     head_dim: int, next_pages: Optional[torch.Tensor] = None,
                     slopes: Optional[torch.Tensor] = None, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                    value_shift: int = 0) -> None:
+                    value_shift: int = 0, value_shifts: int = 1) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
     the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
@@ -1095,12 +1096,27 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     joins the softmax's denominator of head h; it has no key and no value.  ``value_shift`` s: the weights of a head
     whose kv head is c meet the values of kv head (c + s) mod Hkv (a mixer that mixes the heads' weights sums such
     outputs).  Every kernel takes the three (not together with a distance bias or a cache of one plane).
+    ``value_shifts`` S > 1: out is [S, T, Hq D] and entry s is the output for shift s; where the whole step is served by
+    the kernels for few rows, the shifts are one launch (a grid dimension), else one launch each.
 
     ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
     pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     T = qkv.shape[0]
-    _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
+    S = int(value_shifts)
+    if S > 1:
+        _need(value_shift == 0 and S <= Hkv and out.shape == (S, T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype,
+              "paged_attention: several shifts write out [S, T, Hq D], S <= Hkv")
+        plan0 = ctx.attn_plan
+        key0 = plan0.get("geometry_index", {}).get((Hq, Hkv, D, window), plan0.get("geometry_index", {}).get((Hq, Hkv, D, window, False)))
+        one_launch = (SHIFTS_IN_ONE_LAUNCH and key0 is not None and f"fa{key0}_items" in plan0 and f"tc{key0}_items" not in plan0
+                      and plan0[f"fa{key0}_info_host"][0] * Hkv * S <= _MERGE_COUNTERS and kv_pages.shape[1] == 2 and slopes is None)
+        if not one_launch:
+            for s in range(S):
+                paged_attention(qkv, kv_pages, block_tables, ctx, out[s], scale, window, Hq, Hkv, D, next_pages, slopes, softcap, sinks, s)
+            return
+    else:
+        _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
     _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous() and kv_pages.shape[1] in (1, 2),
           "paged_attention: kv_pages must be [pages, 2 (or 1: the values are the keys' channels), Hkv, page, D] in q's dtype")
     planes = int(kv_pages.shape[1])
@@ -1110,7 +1126,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     if slopes is not None:
         _need(slopes.dtype == torch.float32 and slopes.numel() == Hq and slopes.is_contiguous(), "paged_attention: slopes must be float32 [Hq]")
     index = plan.get("geometry_index", {})
-    plain = softcap > 0.0 or sinks is not None or value_shift != 0
+    plain = softcap > 0.0 or sinks is not None or value_shift != 0 or S > 1
     if sinks is not None:
         _need(sinks.dtype == torch.float32 and sinks.numel() == Hq and sinks.is_contiguous(), "paged_attention: sinks must be float32 [Hq]")
     if plain:
@@ -1146,9 +1162,9 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             return                      # every request of the step went to the kernel above
         part_acc = part_ml = None
         if n_parts:
-            part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
-            part_ml = ctx.arena.alloc((n_parts * Hkv * part_rows, 2), torch.float32)
-        counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
+            part_acc = ctx.arena.alloc((S * n_parts * Hkv * part_rows, D), torch.float32)
+            part_ml = ctx.arena.alloc((S * n_parts * Hkv * part_rows, 2), torch.float32)
+        counters = _merge_counters(qkv.device) if 0 < S * n_parts * Hkv <= _MERGE_COUNTERS else None
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
         if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
@@ -1165,9 +1181,9 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _check(lib().qe_decode_attention_mma(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
+                int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv * S <= TC_TARGET_CTAS),
                 ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes,
-                ctypes.c_float(softcap), _ptr(sinks), int(value_shift), _stream()),
+                ctypes.c_float(softcap), _ptr(sinks), int(value_shift), S, ctypes.c_long(T * Hq * D), int(n_parts), _stream()),
                 "decode_attention_mma")
             return
         last_attention_kernel = "flash_attention"
@@ -1176,7 +1192,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), int(small_tiles), ctypes.c_float(scale), int(window),
             Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, ctypes.c_float(softcap), _ptr(sinks), int(value_shift),
-            _stream()), "flash_attention")
+            S, ctypes.c_long(T * Hq * D), int(n_parts), _stream()), "flash_attention")
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2

@@ -295,9 +295,12 @@ class GQAAttention(Mixer):
         gate = proj[:, self.q_width + 2 * self.kv_width:self.q_width + 2 * self.kv_width + H] if self.output_gate else None
         direct = shifts == 1 and gate is None and inner.is_contiguous()
         partial = inner.unsqueeze(0) if direct else ctx.arena.alloc((shifts, T, self.q_width), ctx.dtype)
-        for s in range(shifts):
-            ops.paged_attention(qkv, cache, view.block_tables, ctx, partial[s], self.scale, 0, H, Hkv, D,
-                                softcap=self.softcap or 0.0, sinks=self.sinks, value_shift=s)
+        if shifts > 1:
+            ops.paged_attention(qkv, cache, view.block_tables, ctx, partial, self.scale, 0, H, Hkv, D,
+                                softcap=self.softcap or 0.0, sinks=self.sinks, value_shifts=shifts)
+        else:
+            ops.paged_attention(qkv, cache, view.block_tables, ctx, partial[0], self.scale, 0, H, Hkv, D,
+                                softcap=self.softcap or 0.0, sinks=self.sinks)
         if not direct:
             ops.head_mix_gate(partial, self.head_mix, gate, inner, H, Hkv, D)
 

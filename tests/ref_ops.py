@@ -135,11 +135,15 @@ def plan_attention(q_lens, ctx_lens, page_size, geometries=(), dtype=None, unifo
 
 
 def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim, next_pages=None,
-                    slopes=None, softcap=0.0, sinks=None, value_shift=0):
+                    slopes=None, softcap=0.0, sinks=None, value_shift=0, value_shifts=1):
     """For each request: gather its keys and values from the pages by its block table, then
     softmax(scale q k^T + mask) v with key j allowed for the query at position i iff
     j <= i and (window == 0 or j > i - window)."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    if value_shifts > 1:                  # out [S, T, Hq D]: one output per shift of the values' kv head
+        for s in range(value_shifts):
+            paged_attention(qkv, kv_pages, block_tables, ctx, out[s], scale, window, Hq, Hkv, D, next_pages, slopes, softcap, sinks, s)
+        return
     P = kv_pages.shape[3]
     cu = ctx.cu_q.tolist()
     ctx_lens = ctx.ctx_lens.tolist()

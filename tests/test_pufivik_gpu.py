@@ -281,6 +281,59 @@ def test_long_portions_at_head_size_128_on_the_tensor_memory_kernel(ops, softcap
     assert spy.count("qe_flash_attention_tc") == 1 and spy.count("qe_decode_attention_mma") + spy.count("qe_flash_attention_fused_merge") == 1
 
 
+@pytest.mark.parametrize("H,G,D,P", [(8, 4, 128, 16), (4, 2, 80, 16), (6, 3, 32, 8)])
+def test_all_shifts_of_decoded_tokens_in_one_launch(ops, H, G, D, P):
+    """Steps without a long portion: every shift of the values' kv head as one launch, each with its own output, parts and
+    counters, what one launch per shift gives; contexts short, split into parts, and of a few rows."""
+    from helpers import LaunchSpy
+    from qwen_engine_b200.engine.runner import ModelRunner
+    from qwen_engine_b200.parts.base import Arena
+    g = torch.Generator().manual_seed(D)
+    q_lens, ctx_lens = [1, 1, 3, 1, 2], [0, 2700, 40, 600, 1300]
+    totals = [c + n for c, n in zip(ctx_lens, q_lens)]
+    blocks = [-(-t // P) for t in totals]
+    tables = torch.full((len(q_lens), max(blocks)), -1, dtype=torch.int32)
+    at = 0
+    for r, b in enumerate(blocks):
+        tables[r, :b] = torch.arange(at, at + b, dtype=torch.int32)
+        at += b
+    cache = torch.randn(at, 2, G, P, D, generator=g).to(BF16).to(DEV)
+    T = sum(q_lens)
+    qkv = torch.randn(T, (H + 2 * G) * D, generator=g).to(BF16).to(DEV)
+    sinks = (torch.randn(H, generator=g) * 2.0).to(DEV)
+    geo = (H, G, D, 0)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    outs = []
+    for one in (True, False):
+        ops.SHIFTS_IN_ONE_LAUNCH = one
+        try:
+            for splits in (None, {geo: 4}):
+                plan = ops.plan_attention(q_lens, ctx_lens, P, (geo,), BF16, uniform_splits=splits)
+                devplan = ModelRunner._device_plan(plan, {"plan_" + k: i32(v) for k, v in plan.items()}, (geo,))
+                ctx = SimpleNamespace(cu_q=i32(cu), ctx_lens=i32(ctx_lens), q_lens_host=q_lens, ctx_lens_host=ctx_lens, attn_plan=devplan,
+                                      arena=Arena(DEV, 1 << 26))
+                out = torch.zeros(G, T, H * D, dtype=BF16, device=DEV)
+                with LaunchSpy() as spy:
+                    ops.paged_attention(qkv, cache, tables.to(DEV), ctx, out, D ** -0.5, 0, H, G, D, softcap=5.0, sinks=sinks, value_shifts=G)
+                torch.cuda.synchronize()
+                assert spy.count("qe_decode_attention_mma") + spy.count("qe_flash_attention_fused_merge") == (1 if one else G)
+                outs.append(out.float().cpu())
+        finally:
+            ops.SHIFTS_IN_ONE_LAUNCH = True
+    # (to rounding: with more CTAs in the launch the kernel may take CTAs of fewer warps, which add a context's keys in another order)
+    _close(outs[0], outs[2], BF16, "one launch against one a shift", tol=1e-2)
+    _close(outs[1], outs[3], BF16, "one launch against one a shift, four parts a request", tol=1e-2)
+    want = torch.empty(G, T, H * D, dtype=F32)
+    cpu_ctx = SimpleNamespace(cu_q=torch.tensor(cu), ctx_lens=torch.tensor(ctx_lens))
+    ref_ops.paged_attention(qkv.float().cpu(), cache.float().cpu(), tables, cpu_ctx, want, D ** -0.5, 0, H, G, D, softcap=5.0, sinks=sinks.cpu(),
+                            value_shifts=G)
+    _close(outs[0], want, BF16, "one launch", tol=2e-2)
+    _close(outs[1], want, BF16, "one launch, four parts a request", tol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_single_decoded_tokens_alone_and_from_the_first_token(ops, dtype):
     """Steps of single tokens only (the kernels' layout for few rows, contexts in parts that are merged with the sink):
