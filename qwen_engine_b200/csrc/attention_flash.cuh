@@ -9,6 +9,9 @@
 // bfloat16 before P·V (attn.py:263); the mask is key <= position (and > position - window)
 // (attn.py:195, 239).  Tiles above the causal frontier are never visited.  A mixer may bias the scores by
 // distance: slopes[head] * (position - key) is then taken off each score (float32, before the softmax).
+// Or it may bend them (softcap tanh(score / softcap), float32, ahead of the mask), keep a sink in a head's denominator
+// (exp(sinks[head]), added once where a row is finished: in the direct write or where a split context's parts are
+// merged), and let a head's weights meet the values of another kv head (v_shift).
 //
 // A work item may cover only a range of keys (a split of a long context for a decoded token:
 // flash decoding, attn.py:374-594 with split_size 256); then it writes its unnormalised

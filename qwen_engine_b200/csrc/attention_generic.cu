@@ -10,6 +10,10 @@
 // steps (attn.py:236-267 has the same algebra per BLOCK_N).  Query head h reads kv head
 // h / (Hq / Hkv) (attn.py:181-182).
 //
+// Options of other designs: `softcap` > 0 bends the scaled score s to softcap tanh(s / softcap) ahead of the mask; `sinks`
+// [Hq] adds exp(sinks[h]) to head h's denominator (no key, no value); `v_shift` lets a head whose kv head is c read the
+// values of kv head (c + v_shift) mod Hkv (the keys stay its own).
+//
 // One CTA per (tile of 16 queries of one request, query head); 4 warps, 4 queries each.  Within a
 // warp lane j owns key j of the tile for the scores and dims d = lane + 32 i of the output.
 #include "common.cuh"
